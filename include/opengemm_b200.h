@@ -1,0 +1,124 @@
+/* C ABI of libopengemm_b200.so: a B200 (sm_100a) GEMM library that stands in
+ * for both of OpenGEMM's kernel libraries.
+ *
+ * It exports, with the same names, signatures and status codes, the twelve
+ * entry points the reference's front end binds through ctypes
+ * (opengemm/python/capi.py:86-174): six for the dense library
+ * (opengemm/src/mm/capi.h:9-17, opengemm/src/mm/capi.cu:6-32) and six for the
+ * block-scaled one (opengemm/src/smm/capi.h:9-17, opengemm/src/smm/capi.cu:6-32).
+ * Pointing OPENGEMM_LIB_MM and OPENGEMM_LIB_SMM (opengemm/python/build.py:100-102)
+ * at this one file makes the unmodified reference front end run on it.
+ *
+ * Plain C: pointers and sizes only.  All data pointers are device pointers
+ * owned by the caller; the library keeps no reference to them after a call
+ * returns and allocates no device memory.  Launches are asynchronous on the
+ * stream given.
+ */
+#ifndef OPENGEMM_B200_H
+#define OPENGEMM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define OG_API __declspec(dllexport)
+#else
+#define OG_API __attribute__((visibility("default")))
+#endif
+
+/* opengemm/src/common/abi.h:11 */
+#define OG_ABI_VERSION 3
+
+/* Status codes, opengemm/src/common/abi.h:13-19; OG_ERR_TIMEOUT is new. */
+enum {
+  OG_OK = 0,
+  OG_ERR_BIND = -1,      /* unknown dtype, or a K the format cannot take */
+  OG_ERR_NO_KERNEL = -2, /* no kernel can serve the configuration */
+  OG_ERR_TENSORMAP = -3,
+  OG_ERR_LAUNCH = -4,
+  OG_ERR_TIMEOUT = -5    /* a device-side wait ran out (og_b200_status) */
+};
+
+/* One GEMM: shape, the configs.json entry that picks and drives the kernel,
+ * and the row og_*_bind resolved.  Field for field the reference's struct
+ * (opengemm/src/common/abi.h:24-39), 108 bytes, no padding.  The caller fills
+ * every field but `row`. */
+typedef struct {
+  int32_t m, n, k; /* k in values, not bytes */
+  char dtype[16];  /* "bf16", "e4m3xe5m2", "nvfp4", ... */
+
+  int32_t use_2cta, output_n, use_clc, swap_ab;
+  int32_t cluster_m, cluster_n, cluster_k;
+  int32_t block_m, stages, epi_hold, epi_double, epi_direct;
+  int32_t epi_trade, deep_stages;
+
+  int32_t supergroup, split_k, walk, l2_promo;
+  int32_t persistent;
+
+  int32_t row; /* set by og_*_bind */
+} OgGemm;
+
+/* ---- dense library: replaces opengemm/src/mm/capi.cu:6-32 ---------------- */
+
+/* ABI version this library speaks (mm/capi.cu:6). */
+OG_API int32_t og_mm_abi(void);
+/* Text of the last failure on the calling thread (mm/capi.cu:8). */
+OG_API const char* og_mm_error(void);
+/* Number of kernel rows og_mm_kernel enumerates (mm/capi.cu:10). */
+OG_API int32_t og_mm_kernels(void);
+/* Fill `out` with the configuration that binds to row `i` (mm/capi.cu:12-18). */
+OG_API int32_t og_mm_kernel(int32_t i, OgGemm* out);
+/* Validate dtype / shape / knobs, clamp split_k, set g->row (mm/capi.cu:20, mm/launch.cuh:41-64). */
+OG_API int32_t og_mm_bind(OgGemm* g);
+/* Enqueue C[m,n] = A[m,k] . B[n,k]^T on `stream` of `device` (mm/capi.cu:22-32, mm/launch.cuh:105-183).
+ * sfa and sfb are ignored. */
+OG_API int32_t og_mm_launch(const OgGemm* g, const void* a, const void* b, const void* sfa,
+                            const void* sfb, void* c, int32_t device, void* stream);
+
+/* ---- block-scaled library: replaces opengemm/src/smm/capi.cu:6-32 -------- */
+
+OG_API int32_t og_smm_abi(void);
+OG_API const char* og_smm_error(void);
+OG_API int32_t og_smm_kernels(void);
+OG_API int32_t og_smm_kernel(int32_t i, OgGemm* out);
+/* smm/launch.cuh:38-57 */
+OG_API int32_t og_smm_bind(OgGemm* g);
+/* sfa / sfb: scales in the 128x4 blocked layout (smm/launch.cuh:87-150, smm/tmap.cuh:21-36). */
+OG_API int32_t og_smm_launch(const OgGemm* g, const void* a, const void* b, const void* sfa,
+                             const void* sfb, void* c, int32_t device, void* stream);
+
+/* ---- additions with no counterpart in the reference ----------------------- */
+
+/* The native tile plan of a bound GEMM, for tuners and reports. */
+typedef struct {
+  int32_t cta_group; /* CTAs per MMA: 1 or 2 */
+  int32_t tile_m, tile_n, block_k, stages;
+  int32_t swap;      /* operands exchanged: B rows ride the 128-row MMA side */
+  int32_t epi_tma;   /* epilogue through shared memory + TMA store */
+  int32_t acc_slots; /* accumulator buffers in tensor memory */
+  int32_t tmem_cols, smem_bytes;
+  int32_t tiles, grid; /* output tiles; CTAs launched */
+  int32_t group;     /* rasterisation band width in tiles */
+} OgPlan;
+
+/* Describe how `g` (already bound by og_mm_bind / og_smm_bind) would run on `device`
+ * (pass -1 for "assume 148 SMs", which needs no GPU). */
+OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out);
+
+/* Launch like og_mm_launch / og_smm_launch (chosen by g->dtype) with a device status
+ * word: `status` points to a zero-initialised int32 in device-accessible memory.  A wait
+ * that gives up stores (site | cta << 8) there instead of spinning forever. */
+OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void* b,
+                                      const void* sfa, const void* sfb, void* c, int32_t device,
+                                      void* stream, int32_t* status);
+
+/* Limit of every device-side wait in milliseconds (default 2000). */
+OG_API void og_b200_set_wait_limit_ms(int32_t ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OPENGEMM_B200_H */

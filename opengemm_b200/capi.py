@@ -1,0 +1,221 @@
+"""ctypes binding of libopengemm_b200.so: the C ABI of include/opengemm_b200.h.
+
+Mirrors the reference's binding layer (opengemm/python/capi.py:12-188): the
+`OgGemm` structure, which config keys pick a kernel and which steer a launch,
+`Library(impl)` with `kernels / bind / launch / error`, and the module-level
+`library()` / `bind()`.  One shared object serves both `impl`s here.  There is
+no fallback: a missing or unloadable library raises.
+"""
+
+import ctypes
+import threading
+from ctypes import POINTER, byref, c_char, c_char_p, c_int32, c_void_p
+
+import torch
+
+from . import build
+from .dtypes import DTYPES
+
+ABI_VERSION = 3
+OG_OK, OG_ERR_BIND, OG_ERR_NO_KERNEL, OG_ERR_TENSORMAP, OG_ERR_LAUNCH, OG_ERR_TIMEOUT = 0, -1, -2, -3, -4, -5
+
+_INT_FIELDS_BEFORE = ("m", "n", "k")
+_INT_FIELDS_AFTER = (
+    "use_2cta", "output_n", "use_clc", "swap_ab",
+    "cluster_m", "cluster_n", "cluster_k",
+    "block_m", "stages", "epi_hold", "epi_double", "epi_direct",
+    "epi_trade", "deep_stages",
+    "supergroup", "split_k", "walk", "l2_promo",
+    "persistent",
+    "row",
+)
+
+
+class OgGemm(ctypes.Structure):
+    """One GEMM as the C side sees it (include/opengemm_b200.h, 108 bytes)."""
+
+    _fields_ = (
+        [(f, c_int32) for f in _INT_FIELDS_BEFORE]
+        + [("dtype", c_char * 16)]
+        + [(f, c_int32) for f in _INT_FIELDS_AFTER]
+    )
+
+
+assert ctypes.sizeof(OgGemm) == 108
+
+
+class OgPlan(ctypes.Structure):
+    """The native tile plan of a bound GEMM (og_b200_plan)."""
+
+    _fields_ = [
+        (f, c_int32)
+        for f in (
+            "cta_group", "tile_m", "tile_n", "block_k", "stages", "swap", "epi_tma",
+            "acc_slots", "tmem_cols", "smem_bytes", "tiles", "grid", "group",
+        )
+    ]
+
+
+# Config keys that pick a kernel, and those read at launch, per implementation
+# (the split the reference makes in capi.py:36-67).
+KERNEL_KEYS = {
+    "mm": ("use_2cta", "output_n", "use_clc", "swap_ab", "cluster_m", "cluster_n", "cluster_k",
+           "block_m", "stages", "epi_hold", "epi_double", "epi_direct", "split_k"),
+    "smm": ("use_2cta", "output_n", "use_clc", "swap_ab", "cluster_m", "cluster_n", "cluster_k",
+            "epi_trade", "deep_stages"),
+}
+LAUNCH_KEYS = {
+    "mm": ("supergroup", "walk", "l2_promo"),
+    "smm": ("supergroup", "epi_direct", "persistent"),
+}
+# Defaults for keys an entry may omit (entries written by this build's tuner carry all of them).
+KEY_DEFAULTS = {
+    "use_2cta": 0, "output_n": 128, "use_clc": 0, "swap_ab": 0, "cluster_m": 1, "cluster_n": 1,
+    "cluster_k": 1, "block_m": 128, "stages": 0, "epi_hold": 1, "epi_double": 0, "epi_direct": 0,
+    "split_k": 1, "epi_trade": 0, "deep_stages": 0, "supergroup": 8, "walk": 0, "l2_promo": 0,
+    "persistent": 1,
+}
+
+
+def raw_stream(device):
+    """The current CUDA stream of device index `device` as a raw handle."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(device)
+    except AttributeError:
+        return torch.cuda.current_stream(device).cuda_stream
+
+
+def scale_bytes(d, rows, k):
+    """Bytes of a scale tensor in the 128x4 blocked layout."""
+    from .dtypes import sf_block
+
+    return (-(-rows // 128) * 128) * (-(-k // (sf_block(d) * 4)) * 4)
+
+
+class Library:
+    """The shared library seen through one implementation's six entry points."""
+
+    def __init__(self, impl):
+        self.impl = impl
+        self.path = build.library_path(impl)
+        try:
+            lib = ctypes.CDLL(str(self.path))
+        except OSError as exc:
+            raise RuntimeError(
+                f"cannot load the {impl} kernel library {self.path}: {exc}; there is no CPU fallback"
+            ) from exc
+        self._lib = lib
+        prefix = f"og_{impl}_"
+        sig = {
+            "abi": (c_int32, []),
+            "error": (c_char_p, []),
+            "kernels": (c_int32, []),
+            "kernel": (c_int32, [c_int32, POINTER(OgGemm)]),
+            "bind": (c_int32, [POINTER(OgGemm)]),
+            "launch": (c_int32, [POINTER(OgGemm)] + [c_void_p] * 5 + [c_int32, c_void_p]),
+        }
+        for name, (restype, argtypes) in sig.items():
+            fn = getattr(lib, prefix + name)
+            fn.restype, fn.argtypes = restype, argtypes
+            setattr(self, "_" + name, fn)
+        found = self._abi()
+        if found != ABI_VERSION:
+            raise RuntimeError(
+                f"{impl} library {self.path} is ABI version {found}, this build speaks {ABI_VERSION}; "
+                f"delete it and let it rebuild"
+            )
+        # Additions of this build; absent when OPENGEMM_LIB_* points at another library.
+        self._plan = getattr(lib, "og_b200_plan", None)
+        if self._plan is not None:
+            self._plan.restype, self._plan.argtypes = c_int32, [POINTER(OgGemm), c_int32, POINTER(OgPlan)]
+            self._checked = lib.og_b200_launch_checked
+            self._checked.restype = c_int32
+            self._checked.argtypes = [POINTER(OgGemm)] + [c_void_p] * 5 + [c_int32, c_void_p, c_void_p]
+            self._set_limit = lib.og_b200_set_wait_limit_ms
+            self._set_limit.restype, self._set_limit.argtypes = None, [c_int32]
+        self._kernels = None
+
+    def error(self):
+        return self._error().decode()
+
+    def kernels(self):
+        """Every configuration this library offers, as configs.json dicts with a `dtype` key."""
+        if self._kernels is None:
+            rows = []
+            for i in range(self._kernels_count()):
+                g = OgGemm()
+                self._kernel(i, byref(g))
+                row = {"dtype": g.dtype.decode()}
+                row.update({key: getattr(g, key) for key in KERNEL_KEYS[self.impl]})
+                rows.append(row)
+            self._kernels = rows
+        return self._kernels
+
+    def _kernels_count(self):
+        return self._lib[f"og_{self.impl}_kernels"]()
+
+    def spell(self, row):
+        return " ".join(f"{key}={int(row[key])}" for key in KERNEL_KEYS[self.impl])
+
+    def bind(self, name, m, n, k, config):
+        """Resolve a configs.json entry for a shape.  Returns the OgGemm to launch
+        with; it must not be edited afterwards."""
+        keys = KERNEL_KEYS[self.impl] + LAUNCH_KEYS[self.impl]
+        knobs = {key: int(config.get(key, KEY_DEFAULTS[key])) for key in keys}
+        g = OgGemm(m=m, n=n, k=k, dtype=name.encode(), **knobs)
+        status = self._bind(byref(g))
+        if status == OG_OK:
+            return g
+        message = self.error()
+        if status == OG_ERR_NO_KERNEL:
+            message += f"\n\nrequested: {self.spell({k_: knobs.get(k_, 0) for k_ in KERNEL_KEYS[self.impl]})}"
+        raise RuntimeError(message)
+
+    def launch(self, g, a, b, sfa, sfb, out):
+        """Enqueue the bound kernel on the current stream of the operands' device."""
+        device = a.get_device()
+        status = self._launch(
+            byref(g), a.data_ptr(), b.data_ptr(),
+            0 if sfa is None else sfa.data_ptr(), 0 if sfb is None else sfb.data_ptr(),
+            out.data_ptr(), device, raw_stream(device),
+        )
+        if status != OG_OK:
+            raise RuntimeError(self.error())
+
+    def launch_checked(self, g, a, b, sfa, sfb, out, status_word):
+        """Like `launch`, with a zeroed int32 device tensor that receives a code
+        if any device-side wait gives up."""
+        device = a.get_device()
+        status = self._checked(
+            byref(g), a.data_ptr(), b.data_ptr(),
+            0 if sfa is None else sfa.data_ptr(), 0 if sfb is None else sfb.data_ptr(),
+            out.data_ptr(), device, raw_stream(device), status_word.data_ptr(),
+        )
+        if status != OG_OK:
+            raise RuntimeError(self.error())
+
+    def plan(self, g, device=-1):
+        out = OgPlan()
+        if self._plan(byref(g), device, byref(out)) != OG_OK:
+            raise RuntimeError(self.error())
+        return {name: getattr(out, name) for name, _ in OgPlan._fields_}
+
+    def set_wait_limit_ms(self, ms):
+        self._set_limit(int(ms))
+
+
+_libraries, _lock = {}, threading.Lock()
+
+
+def library(impl):
+    """The loaded library for `impl`, loading it on first use."""
+    with _lock:
+        if impl not in _libraries:
+            _libraries[impl] = Library(impl)
+    return _libraries[impl]
+
+
+def bind(name, m, n, k, config):
+    """`(library, OgGemm)` for a configuration on a shape."""
+    lib = library(DTYPES[name].impl)
+    return lib, lib.bind(name, m, n, k, config)

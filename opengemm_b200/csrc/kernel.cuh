@@ -1,0 +1,403 @@
+// One persistent, warp-specialised GEMM kernel for sm_100a that serves the
+// dense formats and the block-scaled ones:  D[rows_m, rows_n] = X . Y^T with
+// both operands K-major.
+//
+//   warp 0      TMA producer: one elected thread streams X/Y (and scale)
+//               tiles into a ring of shared-memory stages
+//   warp 1      owns tensor memory; one elected thread of the pair's leader
+//               copies scale atoms into tensor memory and issues tcgen05.mma
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, convert, and store
+//               either straight to global memory or through swizzled staging
+//               buffers and per-warp TMA stores
+//
+// It takes the place of the reference's two kernels, mm_gemm_kernel
+// (opengemm/src/mm/kernel.cuh:38-601) and smm_gemm_kernel
+// (opengemm/src/smm/kernel.cuh:6-607).  Differences by design: the tile
+// width, stage count, rasterisation and tensor-memory plan are run-time
+// values carried in GemmParams (the instruction and matrix descriptors are
+// register operands, so only the MMA kind and the pair size are compile
+// time); scales travel in the same stage and on the same barrier as the
+// operand tiles; a pair's CTAs each fetch every byte they need with plain
+// TMA loads (no cluster multicast); every wait is bounded.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace og {
+
+constexpr int MAX_STAGES = 16;
+constexpr int THREADS = 192;
+constexpr int SWIZZLE_ALIGN = 1024;
+constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows of one 128-byte swizzle row
+
+struct alignas(64) GemmParams {
+  CUtensorMap map_x;    // MMA-M side operand, [rows_m, K]
+  CUtensorMap map_y;    // MMA-N side operand, [rows_n, K]
+  CUtensorMap map_d;    // output, boxes of 32 rows x 128 bytes (TMA-store epilogue)
+  CUtensorMap map_sfx;  // scales of the M side, blocked layout seen as [atoms*2, 256] bytes
+  CUtensorMap map_sfy;  // scales of the N side
+  void* d;              // output base pointer
+  int* status;          // device word a timed-out wait reports into (may be null)
+  unsigned long long wait_limit_ns;
+  int rows_m, rows_n, k;  // extents in MMA terms (after any operand swap)
+  int ldd;                // elements between consecutive output rows
+  int transpose_out;      // 1: D is written transposed (MMA row -> output column)
+  int tile_n;             // MMA N: multiple of 16, at most 256
+  int block_k, mma_k;     // K values per stage and per MMA
+  int k_blocks;           // stages of K per tile
+  int stages;
+  int x_bytes, y_bytes;   // shared-memory bytes of one stage's X and Y tiles (per CTA)
+  int stage_bytes;        // stride between stages, a multiple of 1024
+  int tx_bytes;           // bytes credited to a stage's barrier, whole pair
+  int tiles_m, tiles_n, num_tiles, group;
+  unsigned idesc;
+  int acc_slots, acc_stride;   // accumulator ring in tensor memory
+  int sf_col, sf_slots, sf_cols;  // scale ring in tensor memory
+  int tmem_cols;
+  int epi_tma;            // 1: staging + TMA store; 0: direct global stores
+  int vec_ok;             // direct stores may use 16-byte vectors
+  int sf_atoms;           // 512-byte scale atoms per stage per 128-row block
+  int sf_yblocks;         // 128-row blocks of N-side scales per tile (1 or 2)
+  int k_groups;           // atoms along K of the global scale buffers
+  int pdl;                // wait for the previous grid before touching memory
+};
+
+struct TileCoord {
+  int mi, ni;
+};
+
+// Tiles are visited in bands `group` tiles wide along N, N fastest inside a
+// band, so concurrently running clusters share X rows and Y rows in L2.
+__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile) {
+  const int band_tiles = p.tiles_m * p.group;
+  const int band = tile / band_tiles;
+  const int first = band * p.group;
+  const int width = min(p.group, p.tiles_n - first);
+  const int in_band = tile - band * band_tiles;
+  return {in_band / width, first + in_band % width};
+}
+
+template <int KIND, int CTA_GROUP, int OUT_BYTES>
+__global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+  constexpr bool SCALED = kind_scaled(KIND);
+  constexpr int TILE_M = 128 * CTA_GROUP;
+
+  extern __shared__ uint8_t dyn_smem[];
+  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = (CTA_GROUP == 2) ? cluster_cta_rank() : 0u;
+  const int cluster_id = blockIdx.x / CTA_GROUP;
+  const int num_clusters = gridDim.x / CTA_GROUP;
+
+  const uint32_t ring = (smem_u32(dyn_smem) + SWIZZLE_ALIGN - 1) & ~uint32_t(SWIZZLE_ALIGN - 1);
+  const uint32_t epi_base = ring + p.stages * p.stage_bytes;
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * MAX_STAGES;
+  const uint32_t bar_acc_full = bar_empty + 8 * MAX_STAGES;
+  const uint32_t bar_acc_empty = bar_acc_full + 16;
+
+  const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_acc_full + 8 * s, 1);
+      mbar_init(bar_acc_empty + 8 * s, 4 * CTA_GROUP);
+    }
+    abort_flag = 0;
+    mbar_init_fence();
+    prefetch_tmap(&p.map_x);
+    prefetch_tmap(&p.map_y);
+    if (p.epi_tma) prefetch_tmap(&p.map_d);
+    if constexpr (SCALED) {
+      prefetch_tmap(&p.map_sfx);
+      prefetch_tmap(&p.map_sfy);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc<CTA_GROUP>(smem_u32(&tmem_slot), p.tmem_cols);
+    tmem_relinquish<CTA_GROUP>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CTA_GROUP == 2) cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (elect_one()) {
+      if (p.pdl) pdl_wait_prior_grids();
+      const int y_rows = p.tile_n / CTA_GROUP;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
+        const TileCoord t = tile_coord(p, tile);
+        const int row_x = t.mi * TILE_M + int(rank) * 128;
+        const int row_y = t.ni * p.tile_n + int(rank) * y_rows;
+        const int sfx_atom = (row_x >> 7) * p.k_groups;
+        const int sfy_atom = ((t.ni * p.tile_n) >> 7) * p.k_groups;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int stage = it % p.stages;
+          const uint32_t phase = (it / p.stages) & 1;
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, ctx, SITE_PRODUCER_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_local = bar_full + 8 * stage;
+          const uint32_t full = (CTA_GROUP == 2) ? map_to_cta(full_local, 0) : full_local;
+          if (rank == 0) mbar_expect_tx(full_local, p.tx_bytes);
+          const uint32_t sx = ring + stage * p.stage_bytes;
+          const uint32_t sy = sx + p.x_bytes;
+          const int kx = kb * p.block_k;
+          tma_load_2d<CTA_GROUP>(sx, &p.map_x, kx, row_x, full);
+          tma_load_2d<CTA_GROUP>(sy, &p.map_y, kx, row_y, full);
+          if constexpr (SCALED) {
+            const uint32_t ssfx = sy + p.y_bytes;
+            const int katom = kb * p.sf_atoms;
+            tma_load_2d<CTA_GROUP>(ssfx, &p.map_sfx, 0, 2 * (sfx_atom + katom), full);
+            for (int b = 0; b < p.sf_yblocks; ++b)
+              tma_load_2d<CTA_GROUP>(ssfx + (1 + b) * p.sf_atoms * 512, &p.map_sfy, 0,
+                                     2 * (sfy_atom + b * p.k_groups + katom), full);
+          }
+        }
+      }
+      if (!ok && rank == 0) {
+        // Loads already issued still land in this CTA's stages: give each
+        // armed barrier a bounded chance to complete before teardown.
+        const uint32_t issued = it < uint32_t(p.stages) ? it : uint32_t(p.stages);
+        for (uint32_t back = 1; back <= issued; ++back) {
+          const uint32_t j = it - back;
+          const uint64_t start = global_timer_ns();
+          while (!mbar_try_wait(bar_full + 8 * (j % p.stages), (j / p.stages) & 1) &&
+                 global_timer_ns() - start < 1000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (rank == 0 && elect_one()) {
+      uint32_t it = 0;
+      int tile_idx = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters, ++tile_idx) {
+        const int slot = tile_idx % p.acc_slots;
+        const uint32_t use = tile_idx / p.acc_slots;
+        if (!mbar_wait(bar_acc_empty + 8 * slot, (use & 1) ^ 1, ctx, SITE_MMA_ACC_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + slot * p.acc_stride;
+        uint32_t sfy_shift = 0;
+        if constexpr (SCALED) {
+          const TileCoord t = tile_coord(p, tile);
+          sfy_shift = ((t.ni * p.tile_n) & 127) >> 5;  // tile origin inside its 128-row scale block
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int stage = it % p.stages;
+          const uint32_t phase = (it / p.stages) & 1;
+          if (!mbar_wait(bar_full + 8 * stage, phase, ctx, SITE_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sx = ring + stage * p.stage_bytes;
+          const uint32_t sy = sx + p.x_bytes;
+          uint32_t sfx_tmem = 0, sfy_tmem = 0;
+          if constexpr (SCALED) {
+            const uint32_t ssfx = sy + p.y_bytes;
+            sfx_tmem = tmem_base + p.sf_col + (it % p.sf_slots) * p.sf_cols;
+            sfy_tmem = sfx_tmem + 4 * p.sf_atoms;
+            for (int w = 0; w < p.sf_atoms; ++w) {
+              scale_copy<CTA_GROUP>(sfx_tmem + 4 * w, scale_desc(ssfx + 512 * w));
+              for (int b = 0; b < p.sf_yblocks; ++b)
+                scale_copy<CTA_GROUP>(sfy_tmem + 4 * (w * p.sf_yblocks + b),
+                                      scale_desc(ssfx + (1 + b) * p.sf_atoms * 512 + 512 * w));
+            }
+          }
+          const uint64_t dx = operand_desc(sx);
+          const uint64_t dy = operand_desc(sy);
+          const int k_left = p.k - kb * p.block_k;
+#pragma unroll
+          for (int ki = 0; ki < 4; ++ki) {
+            // Past the end of K a stage holds TMA's zero fill; an MMA that
+            // would read only that is skipped.  Each MMA covers 32 bytes of
+            // every row, two 16-byte units of the descriptor's start field.
+            if (ki * p.mma_k < k_left) {
+              const uint32_t acc = (kb | ki) ? 1u : 0u;
+              if constexpr (SCALED) {
+                int atom, id;
+                if constexpr (KIND == KIND_NVF4) {
+                  atom = ki, id = 0;
+                } else if constexpr (KIND == KIND_MXF4) {
+                  atom = ki >> 1, id = (ki & 1) * 2;
+                } else {
+                  atom = 0, id = ki;
+                }
+                mma_scaled<KIND, CTA_GROUP>(d_tmem, dx + 2 * ki, dy + 2 * ki,
+                                            p.idesc | (uint32_t(id) << 29) | (uint32_t(id) << 4),
+                                            sfx_tmem + 4 * atom,
+                                            sfy_tmem + 4 * atom * p.sf_yblocks + sfy_shift, acc);
+              } else {
+                mma_dense<KIND, CTA_GROUP>(d_tmem, dx + 2 * ki, dy + 2 * ki, p.idesc, acc);
+              }
+            }
+          }
+          mma_commit<CTA_GROUP>(bar_empty + 8 * stage);
+        }
+        if (ok) mma_commit<CTA_GROUP>(bar_acc_full + 8 * slot);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // the 32 tensor-memory lanes this warp may read
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const uint32_t acc_empty_leader =
+        (CTA_GROUP == 2) ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
+    const uint32_t my_buf = epi_base + (warp - 2) * 2 * EPI_BUF_BYTES;
+    constexpr int CHUNK = (OUT_BYTES == 2) ? 64 : 32;  // columns per 128-byte staging row
+    int buf_use = 0;
+    bool touched_memory = false;
+    int tile_idx = 0;
+    for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters, ++tile_idx) {
+      const TileCoord t = tile_coord(p, tile);
+      const int slot = tile_idx % p.acc_slots;
+      const uint32_t use = tile_idx / p.acc_slots;
+      const bool ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
+      if (!__all_sync(0xFFFFFFFFu, ready)) break;
+      tc_fence_after_sync();
+      if (p.pdl && !touched_memory) pdl_wait_prior_grids();
+      touched_memory = true;
+
+      const int row0 = t.mi * TILE_M + int(rank) * 128 + quarter * 32;  // first row of this warp
+      const int row = row0 + lane;
+      const int col0 = t.ni * p.tile_n;
+      const uint32_t acc_tmem = tmem_base + lane_base + slot * p.acc_stride;
+
+      for (int c = 0; c < p.tile_n && col0 + c < p.rows_n; c += CHUNK) {
+        const int width = min(CHUNK, p.tile_n - c);
+        uint32_t v[CHUNK];
+        if (width >= 32) tmem_ld_32(acc_tmem + c, v);
+        else tmem_ld_16(acc_tmem + c, v);
+        if constexpr (CHUNK == 64) {
+          if (width > 32) {
+            if (width >= 64) tmem_ld_32(acc_tmem + c + 32, v + 32);
+            else tmem_ld_16(acc_tmem + c + 32, v + 32);
+          }
+        }
+        tmem_ld_wait();
+
+        if (p.epi_tma && width == CHUNK && row0 < p.rows_m) {
+          // Stage 32 rows x 128 bytes with the 128-byte swizzle (16-byte unit
+          // index XOR row%8), then one lane stores the box with TMA, which
+          // clips it at the edges of D.
+          const uint32_t buf = my_buf + (buf_use & 1) * EPI_BUF_BYTES;
+          if (buf_use >= 2) {
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+          }
+          ++buf_use;
+          const uint32_t rowaddr = buf + lane * 128;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            uint32_t w0, w1, w2, w3;
+            if constexpr (OUT_BYTES == 4) {
+              w0 = v[4 * u], w1 = v[4 * u + 1], w2 = v[4 * u + 2], w3 = v[4 * u + 3];
+            } else {
+              w0 = pack_bf16x2(__uint_as_float(v[8 * u]), __uint_as_float(v[8 * u + 1]));
+              w1 = pack_bf16x2(__uint_as_float(v[8 * u + 2]), __uint_as_float(v[8 * u + 3]));
+              w2 = pack_bf16x2(__uint_as_float(v[8 * u + 4]), __uint_as_float(v[8 * u + 5]));
+              w3 = pack_bf16x2(__uint_as_float(v[8 * u + 6]), __uint_as_float(v[8 * u + 7]));
+            }
+            st_shared_v4(rowaddr + ((u ^ (lane & 7)) << 4), w0, w1, w2, w3);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&p.map_d, buf, col0 + c, row0);
+            tma_store_commit();
+          }
+        } else if (!p.transpose_out) {
+          if (row < p.rows_m) {
+            const int gc = col0 + c;
+            if (p.vec_ok && gc + width <= p.rows_n) {
+              if constexpr (OUT_BYTES == 4) {
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.d) +
+                                                      size_t(row) * p.ldd + gc);
+#pragma unroll
+                for (int u = 0; u < CHUNK / 4; ++u)
+                  if (4 * u < width) dst[u] = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+              } else {
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) +
+                                                      size_t(row) * p.ldd + gc);
+#pragma unroll
+                for (int u = 0; u < CHUNK / 8; ++u)
+                  if (8 * u < width)
+                    dst[u] = make_uint4(
+                        pack_bf16x2(__uint_as_float(v[8 * u]), __uint_as_float(v[8 * u + 1])),
+                        pack_bf16x2(__uint_as_float(v[8 * u + 2]), __uint_as_float(v[8 * u + 3])),
+                        pack_bf16x2(__uint_as_float(v[8 * u + 4]), __uint_as_float(v[8 * u + 5])),
+                        pack_bf16x2(__uint_as_float(v[8 * u + 6]), __uint_as_float(v[8 * u + 7])));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < CHUNK; ++j) {
+                if (j < width && gc + j < p.rows_n) {
+                  const size_t at = size_t(row) * p.ldd + gc + j;
+                  if constexpr (OUT_BYTES == 4)
+                    static_cast<uint32_t*>(p.d)[at] = v[j];
+                  else
+                    static_cast<uint16_t*>(p.d)[at] =
+                        uint16_t(pack_bf16x2(__uint_as_float(v[j]), 0.f) & 0xFFFFu);
+                }
+              }
+            }
+          }
+        } else {
+          // Transposed output: this thread's MMA row is an output column, so
+          // the lanes of a warp write consecutive elements of one output row.
+          if (row < p.rows_m) {
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j) {
+              const int orow = col0 + c + j;
+              if (j < width && orow < p.rows_n) {
+                const size_t at = size_t(orow) * p.ldd + row;
+                if constexpr (OUT_BYTES == 4)
+                  static_cast<uint32_t*>(p.d)[at] = v[j];
+                else
+                  static_cast<uint16_t*>(p.d)[at] =
+                      uint16_t(pack_bf16x2(__uint_as_float(v[j]), 0.f) & 0xFFFFu);
+              }
+            }
+          }
+        }
+      }
+      // The accumulator slot is in registers or on its way out: hand it back.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + 8 * slot);
+        else mbar_arrive(bar_acc_empty + 8 * slot);
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CTA_GROUP == 2) cluster_sync_all();
+  tc_fence_after_sync();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc<CTA_GROUP>(tmem_base, p.tmem_cols);
+  }
+}
+
+}  // namespace og

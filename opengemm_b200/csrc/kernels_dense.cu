@@ -1,0 +1,36 @@
+// Instantiations of gemm_kernel for the dense MMA kinds (f16, tf32, i8,
+// f8f6f4), one CTA or a pair per MMA, 32-bit output.
+#include "kernels_common.cuh"
+
+namespace og {
+
+cudaError_t configure_dense(int variant, int smem_bytes) {
+  switch (variant) {
+    case 0: return configure_one<KIND_F16, 1, 4>(smem_bytes);
+    case 1: return configure_one<KIND_F16, 2, 4>(smem_bytes);
+    case 2: return configure_one<KIND_TF32, 1, 4>(smem_bytes);
+    case 3: return configure_one<KIND_TF32, 2, 4>(smem_bytes);
+    case 4: return configure_one<KIND_I8, 1, 4>(smem_bytes);
+    case 5: return configure_one<KIND_I8, 2, 4>(smem_bytes);
+    case 6: return configure_one<KIND_F8F6F4, 1, 4>(smem_bytes);
+    case 7: return configure_one<KIND_F8F6F4, 2, 4>(smem_bytes);
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_dense(int variant, const GemmParams& params, int grid, int smem_bytes,
+                         cudaStream_t stream, bool pdl) {
+  switch (variant) {
+    case 0: return launch_one<KIND_F16, 1, 4>(params, grid, smem_bytes, stream, pdl);
+    case 1: return launch_one<KIND_F16, 2, 4>(params, grid, smem_bytes, stream, pdl);
+    case 2: return launch_one<KIND_TF32, 1, 4>(params, grid, smem_bytes, stream, pdl);
+    case 3: return launch_one<KIND_TF32, 2, 4>(params, grid, smem_bytes, stream, pdl);
+    case 4: return launch_one<KIND_I8, 1, 4>(params, grid, smem_bytes, stream, pdl);
+    case 5: return launch_one<KIND_I8, 2, 4>(params, grid, smem_bytes, stream, pdl);
+    case 6: return launch_one<KIND_F8F6F4, 1, 4>(params, grid, smem_bytes, stream, pdl);
+    case 7: return launch_one<KIND_F8F6F4, 2, 4>(params, grid, smem_bytes, stream, pdl);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace og
