@@ -133,20 +133,27 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
+    // One thread; the loop body is kept to a handful of instructions per
+    // stage (ring position and phase advance by increment, never by division).
     if (elect_one()) {
       if (p.pdl) pdl_wait_prior_grids();
       const int y_rows = p.tile_n / CTA_GROUP;
-      uint32_t it = 0;
+      const uint32_t sfx_off = p.x_bytes + p.y_bytes;
+      const uint32_t sf_block_bytes = p.sf_atoms * 512;
+      const int sf_step = 2 * p.sf_atoms;       // tensor-map rows of scales per stage
+      const int sf_block_step = 2 * p.k_groups; // rows between consecutive 128-row blocks
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t issued = 0;
       bool ok = true;
       for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
         const TileCoord t = tile_coord(p, tile);
         const int row_x = t.mi * TILE_M + int(rank) * 128;
         const int row_y = t.ni * p.tile_n + int(rank) * y_rows;
-        const int sfx_atom = (row_x >> 7) * p.k_groups;
-        const int sfy_atom = ((t.ni * p.tile_n) >> 7) * p.k_groups;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const int stage = it % p.stages;
-          const uint32_t phase = (it / p.stages) & 1;
+        int sfx_row = 2 * (row_x >> 7) * p.k_groups;
+        int sfy_row = 2 * ((t.ni * p.tile_n) >> 7) * p.k_groups;
+        int kx = 0;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, ctx, SITE_PRODUCER_EMPTY)) {
             ok = false;
             break;
@@ -155,42 +162,58 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           const uint32_t full = (CTA_GROUP == 2) ? map_to_cta(full_local, 0) : full_local;
           if (rank == 0) mbar_expect_tx(full_local, p.tx_bytes);
           const uint32_t sx = ring + stage * p.stage_bytes;
-          const uint32_t sy = sx + p.x_bytes;
-          const int kx = kb * p.block_k;
           tma_load_2d<CTA_GROUP>(sx, &p.map_x, kx, row_x, full);
-          tma_load_2d<CTA_GROUP>(sy, &p.map_y, kx, row_y, full);
+          tma_load_2d<CTA_GROUP>(sx + p.x_bytes, &p.map_y, kx, row_y, full);
           if constexpr (SCALED) {
-            const uint32_t ssfx = sy + p.y_bytes;
-            const int katom = kb * p.sf_atoms;
-            tma_load_2d<CTA_GROUP>(ssfx, &p.map_sfx, 0, 2 * (sfx_atom + katom), full);
-            for (int b = 0; b < p.sf_yblocks; ++b)
-              tma_load_2d<CTA_GROUP>(ssfx + (1 + b) * p.sf_atoms * 512, &p.map_sfy, 0,
-                                     2 * (sfy_atom + b * p.k_groups + katom), full);
+            const uint32_t ssfx = sx + sfx_off;
+            tma_load_2d<CTA_GROUP>(ssfx, &p.map_sfx, 0, sfx_row, full);
+            tma_load_2d<CTA_GROUP>(ssfx + sf_block_bytes, &p.map_sfy, 0, sfy_row, full);
+            if (p.sf_yblocks == 2)
+              tma_load_2d<CTA_GROUP>(ssfx + 2 * sf_block_bytes, &p.map_sfy, 0,
+                                     sfy_row + sf_block_step, full);
+            sfx_row += sf_step;
+            sfy_row += sf_step;
           }
+          kx += p.block_k;
+          ++issued;
+          if (++stage == p.stages) stage = 0, phase ^= 1;
         }
       }
       if (!ok && rank == 0) {
         // Loads already issued still land in this CTA's stages: give each
         // armed barrier a bounded chance to complete before teardown.
-        const uint32_t issued = it < uint32_t(p.stages) ? it : uint32_t(p.stages);
-        for (uint32_t back = 1; back <= issued; ++back) {
-          const uint32_t j = it - back;
+        int s = stage;
+        uint32_t ph = phase;
+        const uint32_t pending = issued < uint32_t(p.stages) ? issued : uint32_t(p.stages);
+        for (uint32_t back = 0; back < pending; ++back) {
+          if (--s < 0) s = p.stages - 1, ph ^= 1;
           const uint64_t start = global_timer_ns();
-          while (!mbar_try_wait(bar_full + 8 * (j % p.stages), (j / p.stages) & 1) &&
-                 global_timer_ns() - start < 1000000ull) {
+          while (!mbar_try_wait(bar_full + 8 * s, ph) && global_timer_ns() - start < 1000000ull) {
           }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
+    // One thread of the pair's leader.  Descriptors advance by addition; the
+    // scale copies and the four MMAs of a stage are fully unrolled.
     if (rank == 0 && elect_one()) {
-      uint32_t it = 0;
+      constexpr int SF_ATOMS = KIND == KIND_NVF4 ? 4 : KIND == KIND_MXF4 ? 2 : 1;
+      const uint64_t desc_stage = uint64_t(p.stage_bytes >> 4);
+      const uint64_t dx0 = operand_desc(ring);
+      const uint64_t dy0 = operand_desc(ring + p.x_bytes);
+      const uint64_t dsf0 = scale_desc(ring + p.x_bytes + p.y_bytes);
+      const bool two_yblocks = p.sf_yblocks == 2;
+      const int yb = p.sf_yblocks;
+      int stage = 0;
+      uint32_t phase = 0;
+      uint64_t stage_off = 0;  // stage * (stage_bytes >> 4)
+      uint32_t sf_slot = 0;
       int tile_idx = 0;
       bool ok = true;
       for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters, ++tile_idx) {
-        const int slot = tile_idx % p.acc_slots;
-        const uint32_t use = tile_idx / p.acc_slots;
+        const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
+        const uint32_t use = (p.acc_slots == 2) ? (tile_idx >> 1) : tile_idx;
         if (!mbar_wait(bar_acc_empty + 8 * slot, (use & 1) ^ 1, ctx, SITE_MMA_ACC_EMPTY)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + slot * p.acc_stride;
@@ -199,57 +222,53 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           const TileCoord t = tile_coord(p, tile);
           sfy_shift = ((t.ni * p.tile_n) & 127) >> 5;  // tile origin inside its 128-row scale block
         }
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-          const int stage = it % p.stages;
-          const uint32_t phase = (it / p.stages) & 1;
+        uint32_t accumulate = 0;
+        int k_left = p.k;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, ctx, SITE_MMA_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sx = ring + stage * p.stage_bytes;
-          const uint32_t sy = sx + p.x_bytes;
           uint32_t sfx_tmem = 0, sfy_tmem = 0;
           if constexpr (SCALED) {
-            const uint32_t ssfx = sy + p.y_bytes;
-            sfx_tmem = tmem_base + p.sf_col + (it % p.sf_slots) * p.sf_cols;
-            sfy_tmem = sfx_tmem + 4 * p.sf_atoms;
-            for (int w = 0; w < p.sf_atoms; ++w) {
-              scale_copy<CTA_GROUP>(sfx_tmem + 4 * w, scale_desc(ssfx + 512 * w));
-              for (int b = 0; b < p.sf_yblocks; ++b)
-                scale_copy<CTA_GROUP>(sfy_tmem + 4 * (w * p.sf_yblocks + b),
-                                      scale_desc(ssfx + (1 + b) * p.sf_atoms * 512 + 512 * w));
+            sfx_tmem = tmem_base + p.sf_col + sf_slot * p.sf_cols;
+            sfy_tmem = sfx_tmem + 4 * SF_ATOMS;
+            const uint64_t dsf = dsf0 + stage_off;
+#pragma unroll
+            for (int w = 0; w < SF_ATOMS; ++w) {
+              scale_copy<CTA_GROUP>(sfx_tmem + 4 * w, dsf + 32 * w);
+              scale_copy<CTA_GROUP>(sfy_tmem + 4 * w * yb, dsf + 32 * (SF_ATOMS + w));
+              if (two_yblocks)
+                scale_copy<CTA_GROUP>(sfy_tmem + 4 * w * yb + 4, dsf + 32 * (2 * SF_ATOMS + w));
             }
+            sf_slot = (p.sf_slots == 2) ? (sf_slot ^ 1) : 0;
           }
-          const uint64_t dx = operand_desc(sx);
-          const uint64_t dy = operand_desc(sy);
-          const int k_left = p.k - kb * p.block_k;
+          const uint64_t dx = dx0 + stage_off;
+          const uint64_t dy = dy0 + stage_off;
 #pragma unroll
           for (int ki = 0; ki < 4; ++ki) {
             // Past the end of K a stage holds TMA's zero fill; an MMA that
             // would read only that is skipped.  Each MMA covers 32 bytes of
             // every row, two 16-byte units of the descriptor's start field.
-            if (ki * p.mma_k < k_left) {
-              const uint32_t acc = (kb | ki) ? 1u : 0u;
+            if (ki == 0 || ki * p.mma_k < k_left) {
               if constexpr (SCALED) {
-                int atom, id;
-                if constexpr (KIND == KIND_NVF4) {
-                  atom = ki, id = 0;
-                } else if constexpr (KIND == KIND_MXF4) {
-                  atom = ki >> 1, id = (ki & 1) * 2;
-                } else {
-                  atom = 0, id = ki;
-                }
+                constexpr int NVF4 = KIND == KIND_NVF4, MXF4 = KIND == KIND_MXF4;
+                const int atom = NVF4 ? ki : MXF4 ? (ki >> 1) : 0;
+                const uint32_t id = NVF4 ? 0u : MXF4 ? uint32_t((ki & 1) * 2) : uint32_t(ki);
                 mma_scaled<KIND, CTA_GROUP>(d_tmem, dx + 2 * ki, dy + 2 * ki,
-                                            p.idesc | (uint32_t(id) << 29) | (uint32_t(id) << 4),
-                                            sfx_tmem + 4 * atom,
-                                            sfy_tmem + 4 * atom * p.sf_yblocks + sfy_shift, acc);
+                                            p.idesc | (id << 29) | (id << 4), sfx_tmem + 4 * atom,
+                                            sfy_tmem + 4 * atom * yb + sfy_shift, accumulate);
               } else {
-                mma_dense<KIND, CTA_GROUP>(d_tmem, dx + 2 * ki, dy + 2 * ki, p.idesc, acc);
+                mma_dense<KIND, CTA_GROUP>(d_tmem, dx + 2 * ki, dy + 2 * ki, p.idesc, accumulate);
               }
+              accumulate = 1;
             }
           }
           mma_commit<CTA_GROUP>(bar_empty + 8 * stage);
+          k_left -= p.block_k;
+          stage_off += desc_stage;
+          if (++stage == p.stages) stage = 0, phase ^= 1, stage_off = 0;
         }
         if (ok) mma_commit<CTA_GROUP>(bar_acc_full + 8 * slot);
       }
@@ -267,8 +286,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     int tile_idx = 0;
     for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters, ++tile_idx) {
       const TileCoord t = tile_coord(p, tile);
-      const int slot = tile_idx % p.acc_slots;
-      const uint32_t use = tile_idx / p.acc_slots;
+      const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
+      const uint32_t use = (p.acc_slots == 2) ? (tile_idx >> 1) : tile_idx;
       const bool ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
       if (!__all_sync(0xFFFFFFFFu, ready)) break;
       tc_fence_after_sync();
