@@ -9,8 +9,9 @@ path and runs on a CPU):
 It imports the reference's own `opengemm.python.bench` / `.quant`, builds its
 seeded inputs on the CPU generator (`bench.make_inputs(..., device="cpu")`,
 bench.py:78-97), evaluates its oracle (`bench.reference`, bench.py:125-144)
-and stores inputs and outputs as raw bytes in `gemm_<dtype>.npz`, plus the
-outputs of the packing / quantising helpers in `quant.npz`.  The fixtures
+and stores inputs and outputs as raw bytes in `gemm_<dtype>.npz`, the
+outputs of the packing / quantising helpers in `quant.npz`, and the distinct
+knob sets of its shipped configurations in `reference_config_knobs.json`.  The fixtures
 are what pins this repository's oracle to the reference; nothing at test or
 benchmark time reads the reference checkout.
 """
@@ -91,6 +92,23 @@ def main():
     store["to_blocked.out"] = raw(quant.to_blocked(odd))
     np.savez_compressed(HERE / "quant.npz", **store)
     print("wrote quant.npz")
+
+    # Every distinct (dtype, knob set) of the reference's shipped configs.json
+    # files, with one shape it is stored for: bind() must accept all of them.
+    import json
+
+    from opengemm.python import capi, configs
+
+    knob_sets = {}
+    for impl in ("mm", "smm"):
+        seen = {}
+        for (dtype, m, n, k), cfg in configs.load_configs(impl).items():
+            knobs = {key: int(cfg[key]) for key in capi.KERNEL_KEYS[impl] + capi.LAUNCH_KEYS[impl]}
+            sig = (dtype,) + tuple(sorted(knobs.items()))
+            seen.setdefault(sig, {"dtype": dtype, "m": m, "n": n, "k": k, "config": knobs})
+        knob_sets[impl] = list(seen.values())
+    (HERE / "reference_config_knobs.json").write_text(json.dumps(knob_sets, separators=(",", ":")))
+    print("wrote reference_config_knobs.json")
 
 
 if __name__ == "__main__":

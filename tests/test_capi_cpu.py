@@ -1,0 +1,106 @@
+"""The C ABI without a GPU: the library loads, exports every declared symbol,
+speaks ABI 3, validates like the reference's bind, and plans tiles.  No
+compute call is made here."""
+
+import ctypes
+import json
+import re
+from ctypes import byref
+from pathlib import Path
+
+import pytest
+
+from opengemm_b200 import capi
+from opengemm_b200.configs import heuristic_config
+from opengemm_b200.dtypes import DTYPES
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = ROOT / "include" / "opengemm_b200.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return re.findall(r"OG_API\s+[\w\s\*]+?\b(og_\w+)\s*\(", text)
+
+
+def test_every_declared_symbol_is_exported():
+    lib = ctypes.CDLL(str(capi.library("mm").path))
+    names = declared_symbols()
+    assert len(names) >= 15 and len(set(names)) == len(names)
+    for name in names:
+        assert getattr(lib, name) is not None, name
+
+
+def test_abi_version_and_struct_size():
+    assert ctypes.sizeof(capi.OgGemm) == 108
+    for impl in ("mm", "smm"):
+        assert capi.library(impl)._abi() == 3
+
+
+@pytest.mark.parametrize("impl", ["mm", "smm"])
+def test_every_menu_row_binds(impl):
+    lib = capi.library(impl)
+    rows = lib.kernels()
+    assert rows and {r["dtype"] for r in rows} == {n for n, d in DTYPES.items() if d.impl == impl}
+    for row in rows:
+        g = lib.bind(row["dtype"], 512, 512, 512, row)
+        plan = lib.plan(g)
+        assert plan["stages"] >= 2 and plan["tmem_cols"] <= 512 and plan["smem_bytes"] <= 227 * 1024 - 1024
+        assert plan["cta_group"] == (2 if row["use_2cta"] else 1)
+        assert plan["tile_n"] % 16 == 0 and plan["tile_n"] <= 256
+
+
+def test_bind_errors_match_the_reference_contract():
+    lib = capi.library("mm")
+    g = capi.OgGemm(m=16, n=16, k=64, dtype=b"nope")
+    assert lib._bind(byref(g)) == capi.OG_ERR_BIND and "names no element pair" in lib.error()
+    g = capi.OgGemm(m=0, n=16, k=64, dtype=b"bf16")
+    assert lib._bind(byref(g)) == capi.OG_ERR_BIND and "must be positive" in lib.error()
+    g = capi.OgGemm(m=16, n=16, k=12, dtype=b"bf16")
+    assert lib._bind(byref(g)) == capi.OG_ERR_BIND
+    assert lib.error() == "K = 12 is not a multiple of 8, which the tensor map for bf16 requires"
+    g = capi.OgGemm(m=16, n=16, k=192, dtype=b"e2m1")  # sub-byte dense formats need whole 128-value groups
+    assert lib._bind(byref(g)) == capi.OG_ERR_BIND and "multiple of 128" in lib.error()
+    g = capi.OgGemm(m=16, n=16, k=64, dtype=b"nvfp4")  # a block-scaled name through the dense entry point
+    assert lib._bind(byref(g)) == capi.OG_ERR_BIND and "og_smm_bind" in lib.error()
+    smm = capi.library("smm")
+    g = capi.OgGemm(m=16, n=16, k=48, dtype=b"mxfp8")
+    assert smm._bind(byref(g)) == capi.OG_ERR_BIND and "multiple of 32" in smm.error()
+
+
+def test_launch_before_bind_is_refused():
+    lib = capi.library("mm")
+    g = capi.OgGemm(m=128, n=128, k=128, dtype=b"bf16", output_n=128, row=-1)
+    status = lib._launch(byref(g), 1, 1, 0, 0, 1, 0, 0)  # never reaches the GPU: row does not match
+    assert status == capi.OG_ERR_LAUNCH and "bind it first" in lib.error()
+
+
+def test_split_k_is_clamped_like_the_reference():
+    lib = capi.library("mm")
+    g = lib.bind("bf16", 64, 64, 512, dict(heuristic_config("bf16", 64, 64, 512), split_k=64))
+    assert g.split_k == 4  # never more than ceil(K / 128)
+    g = lib.bind("bf16", 64, 64, 512, dict(heuristic_config("bf16", 64, 64, 512), split_k=8, epi_double=1))
+    assert g.split_k == 1
+
+
+def test_all_shipped_reference_knob_sets_bind(golden_dir):
+    """Every distinct knob set of the reference's own configs.json files binds
+    (keys with no native counterpart are mapped, not refused)."""
+    sets = json.loads((golden_dir / "reference_config_knobs.json").read_text())
+    for impl in ("mm", "smm"):
+        lib = capi.library(impl)
+        assert len(sets[impl]) > 50
+        for e in sets[impl]:
+            g = lib.bind(e["dtype"], e["m"], e["n"], e["k"], e["config"])
+            assert lib.plan(g)["tiles"] >= 1
+
+
+def test_plan_of_the_baseline_configurations():
+    for name, m, n, k in [("bf16", 1024, 1024, 1024), ("e4m3", 4096, 4096, 4096), ("s8", 8192, 8192, 8192),
+                          ("s8", 8192, 1024, 8192), ("nvfp4", 8192, 28672, 8192), ("nvfp4", 8192, 3584, 8192),
+                          ("mxfp4", 64, 57344, 8192), ("mxfp4", 64, 7168, 8192)]:
+        lib, g = capi.bind(name, m, n, k, heuristic_config(name, m, n, k))
+        plan = lib.plan(g)
+        assert plan["grid"] <= 148 and plan["tiles"] >= 1
+        if m <= 64:
+            assert plan["swap"] == 1  # small M rides the MMA's N side

@@ -1,0 +1,126 @@
+"""Host-side logic that needs no GPU: format naming, operand checks, the
+configuration store, the torch packing/quantising helpers against fixtures
+made by the reference, and the N-shard bookkeeping."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import opengemm_b200 as og
+from opengemm_b200 import api, configs, quant, shard
+from opengemm_b200.dtypes import DTYPES, dtype_name, extent, k_of, sf_block
+from oracle import opengemm_oracle as ora
+
+
+def test_public_names_are_the_references():
+    assert set(og.__all__) == {"gemm", "prebuild", "emit_kernel", "run_kernel", "dtype_name", "DTYPES",
+                               "quantize", "to_blocked", "pack", "unpack"}
+    assert list(DTYPES) == list(ora.FORMATS)
+    impl, a, b, bits, out, sf = DTYPES["nvfp4"]
+    assert (impl, bits, out, sf) == ("smm", 4, torch.bfloat16, torch.float8_e4m3fn)
+
+
+def test_dtype_name_rules():
+    bf = torch.zeros((2, 8), dtype=torch.bfloat16)
+    u8 = torch.zeros((2, 8), dtype=torch.uint8)
+    e4 = torch.zeros((2, 16), dtype=torch.float8_e4m3fn)
+    e5 = torch.zeros((2, 16), dtype=torch.float8_e5m2)
+    assert dtype_name(bf, bf) == "bf16"
+    assert dtype_name(e4, e5) == "e4m3xe5m2"
+    assert dtype_name(u8, u8, atype="e2m1") == "e2m1"
+    assert dtype_name(atype="e2m1", sftype="ue4m3") == "nvfp4"
+    assert dtype_name(atype="e2m1", sftype="ue8m0") == "mxfp4"
+    assert dtype_name(e4, e4, torch.zeros(512, dtype=torch.float8_e8m0fnu)) == "mxfp8"
+    with pytest.raises(TypeError, match="names no element"):
+        dtype_name(u8, u8)
+    with pytest.raises(TypeError, match="not a format this build serves"):
+        dtype_name(e5, e4)
+    with pytest.raises(TypeError, match="without operands"):
+        dtype_name()
+    d = DTYPES["e3m2"]
+    assert extent(d, 128) == 96 and k_of(d, 96) == 128
+    assert sf_block(DTYPES["nvfp4"]) == 16 and sf_block(DTYPES["mxfp8"]) == 32
+
+
+def test_operand_checks_raise_the_references_errors():
+    a = torch.zeros((4, 64), dtype=torch.bfloat16)
+    with pytest.raises(TypeError, match="a must be a contiguous 2-D CUDA tensor"):
+        og.gemm(a, a)
+    d = DTYPES["nvfp4"]
+    assert api.scale_bytes(d, 8192, 8192) == 8192 * 512 and api.scale_bytes(d, 64, 8192) == 128 * 512
+    assert api.scale_bytes(DTYPES["mxfp4"], 57344, 8192) == 57344 * 256
+    with pytest.raises(ValueError, match="out must be a contiguous"):
+        api.output(DTYPES["bf16"], 4, 4, torch.zeros((4, 5)), torch.device("cpu"))
+
+
+def test_torch_quant_helpers_match_reference_fixtures(golden_dir):
+    z = np.load(golden_dir / "quant.npz")
+    x = torch.from_numpy(z["x"])
+    for elem in ("e3m2", "e2m3", "e2m1"):
+        assert np.array_equal(quant.pack(x, elem).numpy(), z[f"pack.{elem}"])
+        assert np.array_equal(quant.unpack(torch.from_numpy(z[f"pack.{elem}"]), elem, 256).numpy(), z[f"unpack.{elem}"])
+    assert np.array_equal(quant.round_tf32(x.clone()).numpy(), z["round_tf32"])
+    assert np.array_equal(quant.to_blocked(torch.from_numpy(z["to_blocked.in"])).numpy(), z["to_blocked.out"])
+    for name in ("nvfp4", "mxfp8", "mxfp4"):
+        for tag in ("randn", "rand"):
+            src = torch.from_numpy(z[f"quantize.{name}.{tag}.in"].view(np.int16)).view(torch.bfloat16)
+            packed, scales = quant.quantize(src, name)
+            assert np.array_equal(packed.view(torch.uint8).numpy(), z[f"quantize.{name}.{tag}.packed"])
+            assert np.array_equal(scales.view(torch.uint8).numpy(), z[f"quantize.{name}.{tag}.scales"])
+            assert np.array_equal(quant.to_blocked(scales).view(torch.uint8).numpy(), z[f"quantize.{name}.{tag}.blocked"])
+
+
+def test_config_store_round_trip(tmp_path, monkeypatch):
+    monkeypatch.setenv("OPENGEMM_CONFIGS", str(tmp_path))
+    assert configs.stored_entry("bf16", 96, 96, 96) is None
+    cfg = configs.resolve_config("bf16", 96, 96, 96)  # nothing stored: the heuristic answers
+    assert cfg == configs.heuristic_config("bf16", 96, 96, 96)
+    entry = {"dtype": "bf16", "m": 96, "n": 96, "k": 96, "config": dict(cfg, output_n=32)}
+    path = configs.write_entry("mm", entry)
+    assert path == tmp_path / "tuned_configs.json"
+    assert configs.resolve_config("bf16", 96, 96, 96)["output_n"] == 32
+    configs.write_entry("mm", {"dtype": "bf16", "m": 96, "n": 96, "k": 96, "config": dict(cfg, output_n=48)})
+    configs.write_entry("smm", {"dtype": "nvfp4", "m": 1, "n": 2, "k": 64, "config": None, "unimplementable": "too small"})
+    store = json.loads(path.read_text())
+    assert store["arch"] == "sm_100" and [e["dtype"] for e in store["entries"]] == ["bf16", "nvfp4"]
+    assert configs.resolve_config("bf16", 96, 96, 96)["output_n"] == 48
+    with pytest.raises(ValueError, match="cannot be served: too small"):
+        configs.resolve_config("nvfp4", 1, 2, 64)
+    assert not list(tmp_path.glob("*.tmp"))
+
+
+def test_config_store_reads_a_file_in_the_references_schema(tmp_path, monkeypatch, golden_dir):
+    sets = json.loads((golden_dir / "reference_config_knobs.json").read_text())
+    ref_entry = dict(sets["mm"][0])
+    ref_entry["config"] = {k: bool(v) if k in ("use_2cta", "use_clc", "swap_ab") else v for k, v in ref_entry["config"].items()}
+    (tmp_path / "tuned_configs.json").write_text(json.dumps({"kind": "mm", "arch": "sm_100", "entries": [ref_entry]}))
+    monkeypatch.setenv("OPENGEMM_CONFIGS", str(tmp_path))
+    got = configs.resolve_config(ref_entry["dtype"], ref_entry["m"], ref_entry["n"], ref_entry["k"])
+    assert got == ref_entry["config"]
+
+
+def test_shard_bounds_cover_n_on_block_boundaries():
+    for n in (1024, 3584, 28672, 57344, 8192, 520, 77):
+        for world in (1, 2, 4, 8):
+            spans = [shard.shard_bounds(n, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert all(s[0] % 128 == 0 or s[0] == n for s in spans)  # empty trailing shards start at n
+    with pytest.raises(ValueError):
+        shard.shard_bounds(1024, 4, 4)
+
+
+def test_shard_of_blocked_scales_is_the_blocked_shard():
+    """Cutting the flat blocked buffer on 128-row boundaries equals blocking the cut scales."""
+    rng = np.random.default_rng(0)
+    n, k, name = 640, 512, "nvfp4"
+    raw = rng.integers(1, 120, (n, k // 16)).astype(np.uint8)
+    flat = torch.from_numpy(ora.to_blocked(raw))
+    for world in (2, 4):
+        for rank in range(world):
+            n0, n1 = shard.shard_bounds(n, world, rank)
+            part = shard.shard_scales(flat, name, n, k, world, rank).numpy()
+            assert np.array_equal(part, ora.to_blocked(raw[n0:n1]))
