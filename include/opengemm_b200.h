@@ -11,8 +11,10 @@
  *
  * Plain C: pointers and sizes only.  All data pointers are device pointers
  * owned by the caller; the library keeps no reference to them after a call
- * returns and allocates no device memory.  Launches are asynchronous on the
- * stream given.
+ * returns.  It allocates no device memory, with one exception: the first launch
+ * on a device that asks for the stream-K schedule (split_k >= 2) allocates
+ * that schedule's scratch (about 76 MB) for the life of the process.  Launches
+ * are asynchronous on the stream given.
  */
 #ifndef OPENGEMM_B200_H
 #define OPENGEMM_B200_H
@@ -102,6 +104,7 @@ typedef struct {
   int32_t tmem_cols, smem_bytes;
   int32_t tiles, grid; /* output tiles; CTAs launched */
   int32_t group;     /* rasterisation band width in tiles */
+  int32_t stream_k;  /* K blocks dealt out in equal ranges across tiles (split_k >= 2) */
 } OgPlan;
 
 /* Describe how `g` (already bound by og_mm_bind / og_smm_bind) would run on `device`

@@ -51,7 +51,7 @@ class OgPlan(ctypes.Structure):
         (f, c_int32)
         for f in (
             "cta_group", "tile_m", "tile_n", "block_k", "stages", "swap", "epi_tma",
-            "acc_slots", "tmem_cols", "smem_bytes", "tiles", "grid", "group",
+            "acc_slots", "tmem_cols", "smem_bytes", "tiles", "grid", "group", "stream_k",
         )
     ]
 
@@ -66,7 +66,7 @@ KERNEL_KEYS = {
 }
 LAUNCH_KEYS = {
     "mm": ("supergroup", "walk", "l2_promo"),
-    "smm": ("supergroup", "epi_direct", "persistent"),
+    "smm": ("supergroup", "epi_direct", "persistent", "split_k"),  # split_k: an addition of this build
 }
 # Defaults for keys an entry may omit (entries written by this build's tuner carry all of them).
 KEY_DEFAULTS = {

@@ -12,6 +12,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -138,10 +139,21 @@ int encode_2d(CUtensorMap* out, const void* base, int type, uint64_t dim0, uint6
   return OG_OK;
 }
 
+// Stream-K scratch: partial sums of tiles shared by two clusters, and the
+// flags that publish them.  One region per epilogue warp of a full grid;
+// WORKSPACES of them are used round-robin by successive launches so that a
+// launch never reuses the buffers of one that may still be running (each
+// launch fills the GPU, so no more than two or three can overlap).
+constexpr int WORKSPACES = 4;
+constexpr size_t REGION_BYTES = 32 * 256 * 4;
+
 struct DeviceInfo {
   int sm_count = 0;
   uint64_t configured = 0;  // bit per kernel variant
+  float* partial[WORKSPACES] = {};
+  int* flags[WORKSPACES] = {};
 };
+std::atomic<unsigned> launch_epoch{0};
 std::mutex device_mutex;
 DeviceInfo devices[64];
 
@@ -179,6 +191,40 @@ int ensure_configured(int device, int variant, int smem_bytes) {
   (void)smem_bytes;
   info.configured |= bit;
   return OG_OK;
+}
+
+// The workspace for one stream-K launch on `device` (allocated on first use;
+// flags start at zero and are matched against a per-launch epoch, so they
+// are never cleared).
+int workspace_for(int device, int sm_count, unsigned epoch, float** partial, int** flags) {
+  std::lock_guard<std::mutex> lock(device_mutex);
+  DeviceInfo& info = devices[device & 63];
+  const int slot = int(epoch % WORKSPACES);
+  if (!info.partial[slot]) {
+    const size_t regions = size_t(sm_count) * 4;
+    void* data = nullptr;
+    void* words = nullptr;
+    if (cudaMalloc(&data, regions * REGION_BYTES) != cudaSuccess ||
+        cudaMalloc(&words, regions * sizeof(int)) != cudaSuccess ||
+        cudaMemset(words, 0, regions * sizeof(int)) != cudaSuccess) {
+      cudaGetLastError();
+      if (data) cudaFree(data);
+      if (words) cudaFree(words);
+      return fail(OG_ERR_LAUNCH, "cannot allocate the %zu-byte stream-K workspace", regions * REGION_BYTES);
+    }
+    info.partial[slot] = static_cast<float*>(data);
+    info.flags[slot] = static_cast<int*>(words);
+  }
+  *partial = info.partial[slot];
+  *flags = info.flags[slot];
+  return OG_OK;
+}
+
+// Stream-K pays when the tiles do not fill a whole number of waves and every
+// cluster still gets at least one tile's worth of K blocks.
+bool use_stream_k(const OgGemm& g, const Plan& p, int grid) {
+  const int clusters = grid / p.cta_group;
+  return g.split_k >= 2 && p.num_tiles > clusters && p.num_tiles % clusters != 0;
 }
 
 int grid_for(const Plan& p, int sm_count) {
@@ -293,7 +339,17 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
   params.k_groups = p.k_groups;
   params.pdl = 0;
 
-  const int grid = grid_for(p, sm_count_of(device));
+  const int sm_count = sm_count_of(device);
+  const int grid = grid_for(p, sm_count);
+  if (use_stream_k(*g, p, grid)) {
+    unsigned epoch = ++launch_epoch;
+    if ((epoch & 0x7FFFFFFFu) == 0) epoch = ++launch_epoch;  // the tag is never 0
+    const int got = workspace_for(device, sm_count, epoch, &params.partial, &params.flags);
+    if (got != OG_OK) return got;
+    params.stream_k = 1;
+    params.epoch = int(epoch & 0x7FFFFFFFu);
+    params.acc_int = p.format->out == OUT_S32;
+  }
   const cudaError_t launched =
       launch_variant(p.variant, params, grid, p.smem_bytes, static_cast<cudaStream_t>(stream), false);
   if (launched != cudaSuccess)
@@ -376,6 +432,7 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
   out->tiles = p.num_tiles;
   out->grid = grid_for(p, sm_count_of(device));
   out->group = p.group;
+  out->stream_k = use_stream_k(*g, p, out->grid) ? 1 : 0;
   return OG_OK;
 }
 

@@ -60,6 +60,13 @@ struct alignas(64) GemmParams {
   int sf_yblocks;         // 128-row blocks of N-side scales per tile (1 or 2)
   int k_groups;           // atoms along K of the global scale buffers
   int pdl;                // wait for the previous grid before touching memory
+  // Stream-K: the (tile, K-block) units are dealt out in equal contiguous
+  // ranges, so a range may begin or end inside a tile.  See WorkIter.
+  int stream_k;
+  int acc_int;            // accumulators are s32 (partials add as integers)
+  int epoch;              // this launch's tag in `flags` (never 0)
+  float* partial;         // per epilogue warp: 32 rows x 256 columns of f32 partial sums
+  int* flags;             // per epilogue warp: epoch of the partial it last published
 };
 
 struct TileCoord {
@@ -76,6 +83,53 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile) {
   const int in_band = tile - band * band_tiles;
   return {in_band / width, first + in_band % width};
 }
+
+// One piece of work for a cluster: K blocks [kb0, kb1) of an output tile.
+struct Work {
+  int tile, kb0, kb1;
+};
+
+// The sequence of work of one cluster; all three roles walk it identically.
+//
+// Static schedule: whole tiles cluster, cluster + clusters, ...
+// Stream-K: units u = tile * k_blocks + kb are split into `clusters` equal
+// contiguous ranges (each at least k_blocks long, the host guarantees), so a
+// tile is shared by at most two neighbouring clusters.  The cluster whose
+// range BEGINS inside a tile meets it first: it computes the tile's last K
+// blocks and publishes raw f32/s32 partial sums.  The cluster whose range ENDS
+// inside the tile meets it last: it computes the first K blocks, adds the
+// neighbour's partial and writes the output.  The contributor never waits, so
+// the schedule cannot deadlock while all clusters are resident.
+struct WorkIter {
+  int stream_k, k_blocks, num_tiles, step, tile;
+  long long u, u_end;
+  __device__ __forceinline__ WorkIter(const GemmParams& p, int cluster, int clusters) {
+    stream_k = p.stream_k;
+    k_blocks = p.k_blocks;
+    num_tiles = p.num_tiles;
+    step = clusters;
+    tile = cluster;
+    const long long total = (long long)p.num_tiles * p.k_blocks;
+    u = total * cluster / clusters;
+    u_end = total * (cluster + 1) / clusters;
+  }
+  __device__ __forceinline__ bool next(Work& w) {
+    if (!stream_k) {
+      if (tile >= num_tiles) return false;
+      w = {tile, 0, k_blocks};
+      tile += step;
+      return true;
+    }
+    if (u >= u_end) return false;
+    const int t = int(u / k_blocks);
+    const int kb0 = int(u - (long long)t * k_blocks);
+    const long long left = u_end - u;
+    const int kb1 = left < k_blocks - kb0 ? kb0 + int(left) : k_blocks;
+    w = {t, kb0, kb1};
+    u += kb1 - kb0;
+    return true;
+  }
+};
 
 template <int KIND, int CTA_GROUP, int OUT_BYTES>
 __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
@@ -146,14 +200,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       uint32_t phase = 0;
       uint32_t issued = 0;
       bool ok = true;
-      for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters) {
-        const TileCoord t = tile_coord(p, tile);
+      WorkIter work(p, cluster_id, num_clusters);
+      Work w;
+      while (ok && work.next(w)) {
+        const TileCoord t = tile_coord(p, w.tile);
         const int row_x = t.mi * TILE_M + int(rank) * 128;
         const int row_y = t.ni * p.tile_n + int(rank) * y_rows;
-        int sfx_row = 2 * (row_x >> 7) * p.k_groups;
-        int sfy_row = 2 * ((t.ni * p.tile_n) >> 7) * p.k_groups;
-        int kx = 0;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        int sfx_row = 2 * (row_x >> 7) * p.k_groups + w.kb0 * sf_step;
+        int sfy_row = 2 * ((t.ni * p.tile_n) >> 7) * p.k_groups + w.kb0 * sf_step;
+        int kx = w.kb0 * p.block_k;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, ctx, SITE_PRODUCER_EMPTY)) {
             ok = false;
             break;
@@ -211,7 +267,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       uint32_t sf_slot = 0;
       int tile_idx = 0;
       bool ok = true;
-      for (int tile = cluster_id; ok && tile < p.num_tiles; tile += num_clusters, ++tile_idx) {
+      WorkIter work(p, cluster_id, num_clusters);
+      Work w;
+      for (; ok && work.next(w); ++tile_idx) {
         const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
         const uint32_t use = (p.acc_slots == 2) ? (tile_idx >> 1) : tile_idx;
         if (!mbar_wait(bar_acc_empty + 8 * slot, (use & 1) ^ 1, ctx, SITE_MMA_ACC_EMPTY)) break;
@@ -219,12 +277,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         const uint32_t d_tmem = tmem_base + slot * p.acc_stride;
         uint32_t sfy_shift = 0;
         if constexpr (SCALED) {
-          const TileCoord t = tile_coord(p, tile);
+          const TileCoord t = tile_coord(p, w.tile);
           sfy_shift = ((t.ni * p.tile_n) & 127) >> 5;  // tile origin inside its 128-row scale block
         }
         uint32_t accumulate = 0;
-        int k_left = p.k;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        int k_left = p.k - w.kb0 * p.block_k;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, ctx, SITE_MMA_FULL)) {
             ok = false;
             break;
@@ -284,8 +342,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     int buf_use = 0;
     bool touched_memory = false;
     int tile_idx = 0;
-    for (int tile = cluster_id; tile < p.num_tiles; tile += num_clusters, ++tile_idx) {
-      const TileCoord t = tile_coord(p, tile);
+    // Stream-K bookkeeping: this warp's region of the partial-sum workspace
+    // and its neighbour's (the same warp of the next cluster).
+    const int my_region = (cluster_id * CTA_GROUP + int(rank)) * 4 + quarter;
+    const int next_region = my_region + CTA_GROUP * 4;
+    WorkIter work(p, cluster_id, num_clusters);
+    Work w;
+    for (; work.next(w); ++tile_idx) {
+      const TileCoord t = tile_coord(p, w.tile);
+      const bool contributes = w.kb0 > 0;          // publish partial sums instead of output
+      const bool finishes = w.kb1 < p.k_blocks;    // add the neighbour's partial before storing
       const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
       const uint32_t use = (p.acc_slots == 2) ? (tile_idx >> 1) : tile_idx;
       const bool ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
@@ -311,6 +377,41 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           }
         }
         tmem_ld_wait();
+
+        if (finishes) {
+          // All of the chunk's partial sums are requested before any is used,
+          // so the L2 round trips overlap instead of queueing behind one another.
+          if (c == 0 && !wait_flag(p.flags + next_region, p.epoch, ctx)) break;
+          const uint4* src = reinterpret_cast<const uint4*>(p.partial) +
+                             (size_t(next_region) * 64 + (c >> 2)) * 32 + lane;
+          uint4 q[CHUNK / 4];
+#pragma unroll
+          for (int u = 0; u < CHUNK / 4; ++u)
+            q[u] = (4 * u < width) ? __ldcg(src + u * 32) : make_uint4(0u, 0u, 0u, 0u);
+          if (p.acc_int) {
+#pragma unroll
+            for (int u = 0; u < CHUNK / 4; ++u)
+              v[4 * u] += q[u].x, v[4 * u + 1] += q[u].y, v[4 * u + 2] += q[u].z, v[4 * u + 3] += q[u].w;
+          } else {
+#pragma unroll
+            for (int u = 0; u < CHUNK / 4; ++u) {
+              v[4 * u] = __float_as_uint(__uint_as_float(v[4 * u]) + __uint_as_float(q[u].x));
+              v[4 * u + 1] = __float_as_uint(__uint_as_float(v[4 * u + 1]) + __uint_as_float(q[u].y));
+              v[4 * u + 2] = __float_as_uint(__uint_as_float(v[4 * u + 2]) + __uint_as_float(q[u].z));
+              v[4 * u + 3] = __float_as_uint(__uint_as_float(v[4 * u + 3]) + __uint_as_float(q[u].w));
+            }
+          }
+        }
+        if (contributes) {
+          // Raw accumulators, 16 bytes per lane per vector so a warp writes 512
+          // contiguous bytes: vector g of row `lane` sits at (g * 32 + lane).
+          uint4* dst = reinterpret_cast<uint4*>(p.partial) +
+                       (size_t(my_region) * 64 + (c >> 2)) * 32 + lane;
+#pragma unroll
+          for (int u = 0; u < CHUNK / 4; ++u)
+            if (4 * u < width) __stcg(dst + u * 32, make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]));
+          continue;
+        }
 
         if (p.epi_tma && width == CHUNK && row0 < p.rows_m) {
           // Stage 32 rows x 128 bytes with the 128-byte swizzle (16-byte unit
@@ -396,6 +497,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
             }
           }
         }
+      }
+      if (contributes) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) *reinterpret_cast<volatile int*>(p.flags + my_region) = p.epoch;
       }
       // The accumulator slot is in registers or on its way out: hand it back.
       tc_fence_before_sync();

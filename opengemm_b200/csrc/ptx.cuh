@@ -35,6 +35,7 @@ enum WaitSite : int {
   SITE_MMA_ACC_EMPTY = 3,
   SITE_EPI_ACC_FULL = 4,
   SITE_DRAIN = 5,
+  SITE_PARTIAL_FLAG = 6,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -146,6 +147,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
       return false;
     }
   }
+}
+
+// Wait (whole warp) until a global flag word equals `want`: lane 0 polls, the
+// others join it.  Bounded like mbar_wait; false means give up.
+__device__ __forceinline__ bool wait_flag(const int* flag, int want, const WaitCtx& ctx) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    const volatile int* f = flag;
+    const uint64_t start = global_timer_ns();
+    while (*f != want) {
+      if (*ctx.abort_flag || global_timer_ns() - start > ctx.limit_ns) {
+        if (!*ctx.abort_flag) {
+          *ctx.abort_flag = 1;
+          if (ctx.status) atomicCAS(ctx.status, 0, SITE_PARTIAL_FLAG | (int(blockIdx.x) << 8));
+        }
+        ok = 0;
+        break;
+      }
+    }
+    __threadfence();
+  }
+  ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+  return ok != 0;
 }
 
 // ---- TMA (tensor and bulk copies; never multicast) ----------------------------
