@@ -121,6 +121,23 @@ OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void
 /* Limit of every device-side wait in milliseconds (default 2000). */
 OG_API void og_b200_set_wait_limit_ms(int32_t ms);
 
+/* No counterpart in the reference.  The same launch as og_mm_launch / og_smm_launch
+ * (by g->dtype; bind `g` first) for callers that must not allocate device memory
+ * inside a launch: processes that fixed their memory budget at start-up, code
+ * running under an allocator that owns the rest of the GPU, latency-critical loops
+ * that cannot absorb cudaMalloc's implicit device synchronisation.  It runs the
+ * stream-K schedule out of a fixed workspace that is part of the library image
+ * (about 18.5 MiB held by every GPU that loads the library, until exit) and calls
+ * no allocating routine.  Limits: grids of at most 148 CTAs (a device needing more
+ * partial-sum regions is refused with OG_ERR_LAUNCH and a message); one call at a
+ * time per device, because all calls share the workspace: kernels of two calls
+ * that overlap on the GPU race.  The first call on each device looks up the
+ * workspace's address on that device; make it before any stream capture.
+ * `error_text` (may be null) receives up to `error_text_cap` bytes on failure. */
+OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const void* b,
+                                       const void* sfa, const void* sfb, void* c, int32_t device,
+                                       void* stream, char* error_text, int32_t error_text_cap);
+
 #ifdef __cplusplus
 }
 #endif
