@@ -193,13 +193,23 @@ def oracle_inputs(name, rows_a, n, k):
             np.full((rows_a, k // block), code, np.uint8), np.full((n, k // block), code, np.uint8))
 
 
-def host_threads():
+def use_all_host_threads():
+    """Give the CPU BLAS every host core (launchers such as torch.distributed.run
+    export OMP_NUM_THREADS=1, which would cripple the CPU baseline) and return
+    the thread count in effect."""
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     try:
-        from threadpoolctl import threadpool_info
+        import numpy  # noqa: F401  (loads the BLAS whose pool is resized)
+        from threadpoolctl import threadpool_info, threadpool_limits
 
-        return max([p.get("num_threads", 1) for p in threadpool_info()] or [os.cpu_count() or 1])
+        threadpool_limits(limits=cores)
+        return max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
     except Exception:
-        return os.cpu_count() or 1
+        return 1
+
+
+def host_threads():
+    return use_all_host_threads()
 
 
 def cpu_sample(name, m, n, k, budget_s):
@@ -208,6 +218,7 @@ def cpu_sample(name, m, n, k, budget_s):
     one pass costs about `budget_s`.  Returns (seconds, rows, cols, runner)."""
     from oracle import opengemm_oracle as ora
 
+    use_all_host_threads()
     rows, cols = min(m, 256), min(n, 4096)
     a, b, sfa, sfb = oracle_inputs(name, rows, cols, k)
     t0 = time.perf_counter()

@@ -337,7 +337,8 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
   params.sf_atoms = p.sf_atoms;
   params.sf_yblocks = p.sf_yblocks;
   params.k_groups = p.k_groups;
-  params.pdl = 0;
+  static const bool pdl_enabled = [] { const char* e = getenv("OPENGEMM_PDL"); return !(e && e[0] == '0'); }();
+  params.pdl = pdl_enabled ? 1 : 0;
 
   const int sm_count = sm_count_of(device);
   const int grid = grid_for(p, sm_count);
@@ -351,7 +352,7 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
     params.acc_int = p.format->out == OUT_S32;
   }
   const cudaError_t launched =
-      launch_variant(p.variant, params, grid, p.smem_bytes, static_cast<cudaStream_t>(stream), false);
+      launch_variant(p.variant, params, grid, p.smem_bytes, static_cast<cudaStream_t>(stream), params.pdl != 0);
   if (launched != cudaSuccess)
     return fail(OG_ERR_LAUNCH, "kernel launch failed: %s", cudaGetErrorString(launched));
   return OG_OK;

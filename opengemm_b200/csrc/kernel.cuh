@@ -184,6 +184,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   if constexpr (CTA_GROUP == 2) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  // Programmatic dependent launch: from here on the next kernel in the stream
+  // may start its own set-up on SMs this grid leaves free.  Every thread of
+  // this grid that touches global memory first waits for the previous grid.
+  if (p.pdl && threadIdx.x == 0) pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -511,7 +515,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         else mbar_arrive(bar_acc_empty + 8 * slot);
       }
     }
-    if (lane == 0) tma_store_wait<0>();
+    // Shared memory may be released once the last stores have read it.
+    if (lane == 0) tma_store_wait_read<0>();
   }
 
   // ---------------------------------------------------------------- teardown

@@ -1,0 +1,168 @@
+"""Autotuner for one (dtype, shape): sweep the native tile plans, keep only
+candidates that reproduce the reference product, time them, store the winner
+in the configs.json format and return it.
+
+Counterpart of the reference's tuner (opengemm/python/tune.py:13-165) with the
+same outcome contract - a correctness-gated sweep, ties within 1.5 % going to
+the plainer configuration, the winner written with its measurement - over a
+different space: because tile width, pair size, operand swap, ring depth,
+rasterisation band, epilogue path and the stream-K schedule are run-time
+values here, the sweep is coarse-to-fine (tile geometry first, then the
+launch axes around the leaders) instead of a walk over precompiled kernels.
+
+    python -m opengemm_b200.tune --dtype e4m3 --shape 4096 4096 4096
+"""
+
+import argparse
+
+import torch
+
+from . import capi, harness
+from .configs import heuristic_config, load_shapes, write_entry
+from .dtypes import DTYPES
+from .log import log
+
+TIE = 0.015
+
+
+def base_config(name, **knobs):
+    d = DTYPES[name]
+    config = {"use_2cta": False, "output_n": 128, "use_clc": False, "supergroup": 8, "swap_ab": False,
+              "epi_direct": 0, "cluster_m": 1, "cluster_n": 1, "cluster_k": 1, "split_k": 1}
+    if d.impl == "smm":
+        config.update({"epi_trade": 0, "deep_stages": 0, "persistent": 1})
+    else:
+        config.update({"block_m": 128, "stages": 0, "epi_hold": 1, "epi_double": 0, "walk": 0, "l2_promo": 0})
+    config.update(knobs)
+    config["cluster_m"] = 2 if config["use_2cta"] else 1
+    return config
+
+
+def geometry_candidates(name, m, n, k):
+    """Tile geometries worth timing: pair or single CTA x tile width x operand swap."""
+    scaled = DTYPES[name].impl == "smm"
+    widths = (64, 128, 192, 256) if scaled else (32, 64, 96, 128, 160, 192, 224, 256)
+    out = []
+    for swap in ((False, True) if m <= 256 else (False,)):
+        rows_m, rows_n = (n, m) if swap else (m, n)
+        cap = -(-rows_n // 16) * 16
+        fit = sorted({min(w, max(cap, 64 if scaled and rows_n > 32 else 16)) for w in widths} | ({cap} if cap <= 256 and not scaled else set()))
+        for two in (True, False):
+            if two and rows_m <= 128:
+                continue
+            for width in fit:
+                if rows_n >= 1024 and width < 64:
+                    continue
+                if two and width < 32:
+                    continue
+                out.append(base_config(name, use_2cta=two, output_n=int(width), swap_ab=swap))
+    return out
+
+
+def refinements(config, tiles_n):
+    """Launch-axis variations around a leading geometry, one axis at a time."""
+    out = []
+    for band in sorted({1, 2, 4, 16, tiles_n} - {config["supergroup"]}):
+        if 1 <= band <= max(tiles_n, 1):
+            out.append(dict(config, supergroup=band))
+    out.append(dict(config, split_k=2))
+    if not config["swap_ab"]:
+        out.append(dict(config, epi_direct=1))
+    if "l2_promo" in config:
+        out.append(dict(config, l2_promo=2))
+    return out
+
+
+def simplicity(config):
+    """Sort key under which the plainer configuration wins a tie."""
+    return (config["swap_ab"], 0 if config.get("split_k", 1) <= 1 else 1, config.get("epi_direct", 0),
+            config.get("l2_promo", 0), int(config["use_2cta"]), config["output_n"], config["supergroup"])
+
+
+def label(config):
+    text = f"v{2 if config['use_2cta'] else 1} n{config['output_n']:<3} sg{config['supergroup']:<2} swap{int(config['swap_ab'])}"
+    for key in ("split_k", "epi_direct", "l2_promo", "stages"):
+        if config.get(key, 0) not in (0, 1) or (key == "epi_direct" and config.get(key)):
+            text += f" {key}{config[key]}"
+    return text
+
+
+def tune(name, m, n, k, verbose=False, window_ms=15.0):
+    """Sweep one (dtype, shape), store the winner and return its configuration.
+
+    Raises:
+        RuntimeError: if no candidate is correct, or the format cannot take this K.
+    """
+    impl = DTYPES[name].impl
+    buffers = harness.make_input_set(m, n, k, name)
+    want = harness.reference(buffers[0], name)
+    space = geometry_candidates(name, m, n, k)
+    log(f"tuning {name} {m}x{n}x{k} on {harness.env_stamp()['gpu']}: {len(space)} tile geometries")
+
+    ranked, rejected, seen = [], 0, set()
+
+    def measure(config):
+        nonlocal rejected
+        key = tuple(sorted(config.items()))
+        if key in seen:
+            return
+        seen.add(key)
+        try:
+            bound = capi.bind(name, m, n, k, config)
+        except RuntimeError:
+            return
+        if harness.correctness_error(buffers, bound, name, k, want=want):
+            rejected += 1
+            return
+        us = harness.timed(harness.runner(buffers, bound), window_ms=window_ms)
+        ranked.append((us, config))
+        if verbose:
+            log(f"  {label(config):40s} {us:9.2f} us")
+
+    for config in space:
+        measure(config)
+    if not ranked:
+        raise RuntimeError(f"no correct candidate for {name} {m}x{n}x{k}")
+    for _, leader in sorted(ranked, key=lambda row: row[0])[:3]:
+        rows_n = m if leader["swap_ab"] else n
+        for config in refinements(leader, -(-rows_n // leader["output_n"])):
+            measure(config)
+
+    ranked.sort(key=lambda row: row[0])
+    fastest = ranked[0][0]
+    best = min((row for row in ranked if row[0] <= fastest * (1 + TIE)), key=lambda row: simplicity(row[1]))[1]
+
+    kernel = harness.runner(buffers, capi.bind(name, m, n, k, best))
+    us = harness.timed(kernel, window_ms=100.0, repeats=5)
+    baseline, why = harness.baseline_for(buffers, name)
+    base = harness.timed(baseline, window_ms=100.0, repeats=5) if baseline else None
+    log(f"best: {label(best)}  ({len(ranked)} timed, {rejected} failed correctness)")
+    measured = {"us": round(us, 3), "cublas_us": base and round(base, 3), "env": harness.env_stamp()}
+    path = write_entry(impl, {"dtype": name, "m": m, "n": n, "k": k, "config": best, "measured": measured})
+    if base:
+        log(f"kernel {us:.2f}us  cuBLAS {base:.2f}us  {base / us:.3f}x; stored in {path}")
+    else:
+        log(f"kernel {us:.2f}us  no baseline: {why}; stored in {path}")
+    from . import api
+
+    api.forget(name)
+    return best
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--dtype", required=True, choices=sorted(DTYPES))
+    group = parser.add_mutually_exclusive_group(required=True)
+    group.add_argument("--shape", nargs=3, type=int, metavar=("M", "N", "K"))
+    group.add_argument("--all", action="store_true", help="every shape in shapes.jsonc")
+    parser.add_argument("--verbose", action="store_true")
+    args = parser.parse_args()
+    for m, n, k in [tuple(args.shape)] if args.shape else load_shapes():
+        try:
+            tune(args.dtype, m, n, k, verbose=args.verbose)
+        except RuntimeError as exc:
+            print(exc, flush=True)
+
+
+if __name__ == "__main__":
+    main()
