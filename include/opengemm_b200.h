@@ -118,6 +118,11 @@ OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void
                                       const void* sfa, const void* sfb, void* c, int32_t device,
                                       void* stream, int32_t* status);
 
+/* The complete tile plan of a bound `g` for a device of `sm_count` SMs, as one JSON
+ * object of integers written to `out` (what the standalone-kernel emitter bakes
+ * into the code it writes).  Needs no GPU. */
+OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, int32_t cap);
+
 /* Limit of every device-side wait in milliseconds (default 2000). */
 OG_API void og_b200_set_wait_limit_ms(int32_t ms);
 

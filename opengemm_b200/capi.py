@@ -133,6 +133,9 @@ class Library:
             self._checked.argtypes = [POINTER(OgGemm)] + [c_void_p] * 5 + [c_int32, c_void_p, c_void_p]
             self._set_limit = lib.og_b200_set_wait_limit_ms
             self._set_limit.restype, self._set_limit.argtypes = None, [c_int32]
+            self._describe = lib.og_b200_describe
+            self._describe.restype = c_int32
+            self._describe.argtypes = [POINTER(OgGemm), c_int32, c_char_p, c_int32]
         self._kernels = None
 
     def error(self):
@@ -199,6 +202,15 @@ class Library:
         if self._plan(byref(g), device, byref(out)) != OG_OK:
             raise RuntimeError(self.error())
         return {name: getattr(out, name) for name, _ in OgPlan._fields_}
+
+    def describe(self, g, sm_count=148):
+        """Every field of the tile plan of a bound OgGemm, as a dict of ints."""
+        import json
+
+        text = ctypes.create_string_buffer(2048)
+        if self._describe(byref(g), sm_count, text, len(text)) != OG_OK:
+            raise RuntimeError(self.error())
+        return json.loads(text.value.decode())
 
     def set_wait_limit_ms(self, ms):
         self._set_limit(int(ms))

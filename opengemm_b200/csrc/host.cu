@@ -443,6 +443,31 @@ OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void
   return launch_impl(g, a, b, sfa, sfb, c, device, stream, status, -1);
 }
 
+OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, int32_t cap) {
+  if (!g || !out || cap <= 0) return fail(OG_ERR_BIND, "null argument");
+  Plan p;
+  char why[256];
+  const int status = make_plan(*g, sm_count, &p, why, sizeof why);
+  if (status != OG_OK) return fail(status, "%s", why);
+  const int grid = grid_for(p, sm_count > 0 ? sm_count : 148);
+  const int wrote = snprintf(
+      out, size_t(cap),
+      "{\"scaled\":%d,\"variant\":%d,\"kind\":%d,\"cta_group\":%d,\"swap\":%d,\"rows_m\":%d,\"rows_n\":%d,\"k\":%d,"
+      "\"tile_m\":%d,\"tile_n\":%d,\"block_k\":%d,\"mma_k\":%d,\"k_blocks\":%d,\"stages\":%d,\"x_bytes\":%d,"
+      "\"y_bytes\":%d,\"sf_bytes\":%d,\"stage_bytes\":%d,\"tx_bytes\":%d,\"tiles_m\":%d,\"tiles_n\":%d,"
+      "\"num_tiles\":%d,\"group\":%d,\"idesc\":%u,\"acc_slots\":%d,\"acc_stride\":%d,\"sf_col\":%d,\"sf_slots\":%d,"
+      "\"sf_cols\":%d,\"tmem_cols\":%d,\"epi_tma\":%d,\"out_bytes\":%d,\"out\":%d,\"sf_atoms\":%d,\"sf_yblocks\":%d,"
+      "\"k_groups\":%d,\"smem_bytes\":%d,\"x_bits\":%d,\"y_bits\":%d,\"x_map\":%d,\"y_map\":%d,\"l2_promo\":%d,"
+      "\"grid\":%d,\"m\":%d,\"n\":%d}",
+      int(p.format->scaled), p.variant, p.format->kind, p.cta_group, p.swap, p.rows_m, p.rows_n, p.k, p.tile_m,
+      p.tile_n, p.block_k, p.mma_k, p.k_blocks, p.stages, p.x_bytes, p.y_bytes, p.sf_bytes, p.stage_bytes,
+      p.tx_bytes, p.tiles_m, p.tiles_n, p.num_tiles, p.group, p.idesc, p.acc_slots, p.acc_stride, p.sf_col,
+      p.sf_slots, p.sf_cols, p.tmem_cols, p.epi_tma, p.out_bytes, p.format->out, p.sf_atoms, p.sf_yblocks,
+      p.k_groups, p.smem_bytes, p.x_bits, p.y_bits, p.x_map, p.y_map, p.l2_promo, grid, g->m, g->n);
+  if (wrote < 0 || wrote >= cap) return fail(OG_ERR_BIND, "the buffer of %d bytes is too small for the description", cap);
+  return OG_OK;
+}
+
 OG_API void og_b200_set_wait_limit_ms(int32_t ms) {
   wait_limit_ns.store((long long)std::max(1, (int)ms) * 1000000ll);
 }

@@ -132,7 +132,17 @@ struct WorkIter {
 };
 
 template <int KIND, int CTA_GROUP, int OUT_BYTES>
-__global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams params) {
+  // `p` is the scalar view of the launch parameters.  A standalone kernel
+  // emitted for one shape defines OG_FIXED_PLAN to overwrite the plan fields
+  // of a local copy with literals, which lets the compiler fold them; tensor
+  // maps are always addressed in `params`, where TMA needs them.
+#ifdef OG_FIXED_PLAN
+  GemmParams p = params;
+  OG_FIXED_PLAN(p);
+#else
+  const GemmParams& p = params;
+#endif
   constexpr bool SCALED = kind_scaled(KIND);
   constexpr int TILE_M = 128 * CTA_GROUP;
 
@@ -167,12 +177,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     }
     abort_flag = 0;
     mbar_init_fence();
-    prefetch_tmap(&p.map_x);
-    prefetch_tmap(&p.map_y);
-    if (p.epi_tma) prefetch_tmap(&p.map_d);
+    prefetch_tmap(&params.map_x);
+    prefetch_tmap(&params.map_y);
+    if (p.epi_tma) prefetch_tmap(&params.map_d);
     if constexpr (SCALED) {
-      prefetch_tmap(&p.map_sfx);
-      prefetch_tmap(&p.map_sfy);
+      prefetch_tmap(&params.map_sfx);
+      prefetch_tmap(&params.map_sfy);
     }
   }
   if (warp == 1) {
@@ -222,14 +232,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           const uint32_t full = (CTA_GROUP == 2) ? map_to_cta(full_local, 0) : full_local;
           if (rank == 0) mbar_expect_tx(full_local, p.tx_bytes);
           const uint32_t sx = ring + stage * p.stage_bytes;
-          tma_load_2d<CTA_GROUP>(sx, &p.map_x, kx, row_x, full);
-          tma_load_2d<CTA_GROUP>(sx + p.x_bytes, &p.map_y, kx, row_y, full);
+          tma_load_2d<CTA_GROUP>(sx, &params.map_x, kx, row_x, full);
+          tma_load_2d<CTA_GROUP>(sx + p.x_bytes, &params.map_y, kx, row_y, full);
           if constexpr (SCALED) {
             const uint32_t ssfx = sx + sfx_off;
-            tma_load_2d<CTA_GROUP>(ssfx, &p.map_sfx, 0, sfx_row, full);
-            tma_load_2d<CTA_GROUP>(ssfx + sf_block_bytes, &p.map_sfy, 0, sfy_row, full);
+            tma_load_2d<CTA_GROUP>(ssfx, &params.map_sfx, 0, sfx_row, full);
+            tma_load_2d<CTA_GROUP>(ssfx + sf_block_bytes, &params.map_sfy, 0, sfy_row, full);
             if (p.sf_yblocks == 2)
-              tma_load_2d<CTA_GROUP>(ssfx + 2 * sf_block_bytes, &p.map_sfy, 0,
+              tma_load_2d<CTA_GROUP>(ssfx + 2 * sf_block_bytes, &params.map_sfy, 0,
                                      sfy_row + sf_block_step, full);
             sfx_row += sf_step;
             sfy_row += sf_step;
@@ -444,7 +454,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&p.map_d, buf, col0 + c, row0);
+            tma_store_2d(&params.map_d, buf, col0 + c, row0);
             tma_store_commit();
           }
         } else if (!p.transpose_out) {
