@@ -220,15 +220,17 @@ int workspace_for(int device, int sm_count, unsigned epoch, float** partial, int
   return OG_OK;
 }
 
-// Stream-K pays when the tiles do not fill a whole number of waves and every
-// cluster still gets at least one tile's worth of K blocks.
+// Stream-K applies when the tiles do not fill a whole number of waves: the
+// tiles of the partial wave are then cut along K across all clusters.
 bool use_stream_k(const OgGemm& g, const Plan& p, int grid) {
   const int clusters = grid / p.cta_group;
-  return g.split_k >= 2 && p.num_tiles > clusters && p.num_tiles % clusters != 0;
+  return g.split_k >= 2 && p.num_tiles % clusters != 0 && p.k_blocks > 1;
 }
 
-int grid_for(const Plan& p, int sm_count) {
-  const int clusters = std::max(1, std::min(p.num_tiles, sm_count / p.cta_group));
+int grid_for(const Plan& p, int sm_count, bool fill = false) {
+  // `fill`: a stream-K launch occupies every SM even with fewer tiles than SMs.
+  const int all = std::max(1, sm_count / p.cta_group);
+  const int clusters = fill ? std::min(all, std::max(1, p.num_tiles * p.k_blocks)) : std::max(1, std::min(p.num_tiles, all));
   return clusters * p.cta_group;
 }
 
@@ -341,13 +343,21 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
   params.pdl = pdl_enabled ? 1 : 0;
 
   const int sm_count = sm_count_of(device);
-  const int grid = grid_for(p, sm_count);
-  if (use_stream_k(*g, p, grid)) {
+  int grid = grid_for(p, sm_count);
+  if (g->split_k >= 2 && use_stream_k(*g, p, grid_for(p, sm_count, true))) {
+    grid = grid_for(p, sm_count, true);
     unsigned epoch = ++launch_epoch;
     if ((epoch & 0x7FFFFFFFu) == 0) epoch = ++launch_epoch;  // the tag is never 0
     const int got = workspace_for(device, sm_count, epoch, &params.partial, &params.flags);
     if (got != OG_OK) return got;
     params.stream_k = 1;
+    {
+      // split_k is the most ways a tile of the partial wave is cut: that many
+      // clusters per leftover tile share its K blocks, the rest sit the wave out.
+      const int clusters = grid / p.cta_group;
+      const int leftover = p.num_tiles % clusters;
+      params.sk_clusters = std::min<long long>(clusters, (long long)leftover * std::min<int>(g->split_k, p.k_blocks));
+    }
     params.epoch = int(epoch & 0x7FFFFFFFu);
     params.acc_int = p.format->out == OUT_S32;
   }
@@ -433,7 +443,11 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
   out->tiles = p.num_tiles;
   out->grid = grid_for(p, sm_count_of(device));
   out->group = p.group;
-  out->stream_k = use_stream_k(*g, p, out->grid) ? 1 : 0;
+  out->stream_k = 0;
+  if (g->split_k >= 2 && use_stream_k(*g, p, grid_for(p, sm_count_of(device), true))) {
+    out->grid = grid_for(p, sm_count_of(device), true);
+    out->stream_k = 1;
+  }
   return OG_OK;
 }
 

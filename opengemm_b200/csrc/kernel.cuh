@@ -63,6 +63,7 @@ struct alignas(64) GemmParams {
   // Stream-K: the (tile, K-block) units are dealt out in equal contiguous
   // ranges, so a range may begin or end inside a tile.  See WorkIter.
   int stream_k;
+  int sk_clusters;        // clusters that share the partial wave's units (the rest only run whole tiles)
   int acc_int;            // accumulators are s32 (partials add as integers)
   int epoch;              // this launch's tag in `flags` (never 0)
   float* partial;         // per epilogue warp: 32 rows x 256 columns of f32 partial sums
@@ -92,30 +93,39 @@ struct Work {
 // The sequence of work of one cluster; all three roles walk it identically.
 //
 // Static schedule: whole tiles cluster, cluster + clusters, ...
-// Stream-K: units u = tile * k_blocks + kb are split into `clusters` equal
-// contiguous ranges (each at least k_blocks long, the host guarantees), so a
-// tile is shared by at most two neighbouring clusters.  The cluster whose
-// range BEGINS inside a tile meets it first: it computes the tile's last K
-// blocks and publishes raw f32/s32 partial sums.  The cluster whose range ENDS
-// inside the tile meets it last: it computes the first K blocks, adds the
-// neighbour's partial and writes the output.  The contributor never waits, so
-// the schedule cannot deadlock while all clusters are resident.
+//
+// Stream-K schedule: the whole waves of tiles are still dealt out statically
+// (neighbouring clusters then work on neighbouring tiles, which keeps operand
+// panels shared in L2).  Only the tiles of the last, partial wave are cut
+// along K: their units u = tile * k_blocks + kb are split into `clusters`
+// equal contiguous ranges, so such a tile is shared by two or more
+// consecutive clusters.  The cluster holding a tile's first K blocks
+// (kb0 == 0) finishes it: it adds the partial sums of the clusters after it
+// and writes the output.  Every other sharer contributes: it publishes raw
+// f32/s32 partial sums in its own workspace region and never waits, so the
+// schedule cannot deadlock while all clusters are resident.  A range starts
+// inside at most one tile, so a cluster contributes at most once per launch.
 struct WorkIter {
-  int stream_k, k_blocks, num_tiles, step, tile;
-  long long u, u_end;
-  __device__ __forceinline__ WorkIter(const GemmParams& p, int cluster, int clusters) {
+  int stream_k, k_blocks, clusters, cluster, step;
+  int tile, static_tiles;
+  long long total, u, u_end;
+  // `clusters` below is the number of clusters that share the partial wave
+  // (p.sk_clusters, at most the grid's); `step` is the grid's cluster count.
+  __device__ __forceinline__ WorkIter(const GemmParams& p, int cluster_, int grid_clusters) {
     stream_k = p.stream_k;
     k_blocks = p.k_blocks;
-    num_tiles = p.num_tiles;
-    step = clusters;
-    tile = cluster;
-    const long long total = (long long)p.num_tiles * p.k_blocks;
-    u = total * cluster / clusters;
-    u_end = total * (cluster + 1) / clusters;
+    step = grid_clusters;
+    clusters = stream_k ? p.sk_clusters : grid_clusters;
+    cluster = cluster_;
+    tile = cluster_;
+    static_tiles = stream_k ? (p.num_tiles / grid_clusters) * grid_clusters : p.num_tiles;
+    total = (long long)(p.num_tiles - static_tiles) * p.k_blocks;
+    const bool shares = cluster_ < clusters;
+    u = shares ? total * cluster_ / clusters : 0;
+    u_end = shares ? total * (cluster_ + 1) / clusters : 0;
   }
   __device__ __forceinline__ bool next(Work& w) {
-    if (!stream_k) {
-      if (tile >= num_tiles) return false;
+    if (tile < static_tiles) {
       w = {tile, 0, k_blocks};
       tile += step;
       return true;
@@ -125,9 +135,22 @@ struct WorkIter {
     const int kb0 = int(u - (long long)t * k_blocks);
     const long long left = u_end - u;
     const int kb1 = left < k_blocks - kb0 ? kb0 + int(left) : k_blocks;
-    w = {t, kb0, kb1};
+    w = {static_tiles + t, kb0, kb1};
     u += kb1 - kb0;
     return true;
+  }
+  // For the finisher of `w` (kb0 == 0, kb1 < k_blocks): the last cluster
+  // after this one whose range starts inside the same tile.  Clusters in
+  // between may hold an empty range (fewer units than clusters); has_work
+  // tells which ones actually contribute.
+  __device__ __forceinline__ int last_sharer(const Work& w) const {
+    const long long tile_end = (long long)(w.tile - static_tiles + 1) * k_blocks;
+    int last = cluster;
+    for (int j = cluster + 1; j < clusters && total * j / clusters < tile_end; ++j) last = j;
+    return last;
+  }
+  __device__ __forceinline__ bool has_work(int j) const {
+    return total * (j + 1) / clusters > total * j / clusters;
   }
 };
 
@@ -359,13 +382,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     // Stream-K bookkeeping: this warp's region of the partial-sum workspace
     // and its neighbour's (the same warp of the next cluster).
     const int my_region = (cluster_id * CTA_GROUP + int(rank)) * 4 + quarter;
-    const int next_region = my_region + CTA_GROUP * 4;
+    int last_sharer = 0;  // last cluster after this one that shares the tile being finished
     WorkIter work(p, cluster_id, num_clusters);
     Work w;
     for (; work.next(w); ++tile_idx) {
       const TileCoord t = tile_coord(p, w.tile);
       const bool contributes = w.kb0 > 0;          // publish partial sums instead of output
-      const bool finishes = w.kb1 < p.k_blocks;    // add the neighbour's partial before storing
+      const bool finishes = !contributes && w.kb1 < p.k_blocks;  // add the sharers' partials before storing
       const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
       const uint32_t use = (p.acc_slots == 2) ? (tile_idx >> 1) : tile_idx;
       const bool ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
@@ -393,26 +416,37 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         tmem_ld_wait();
 
         if (finishes) {
-          // All of the chunk's partial sums are requested before any is used,
-          // so the L2 round trips overlap instead of queueing behind one another.
-          if (c == 0 && !wait_flag(p.flags + next_region, p.epoch, ctx)) break;
-          const uint4* src = reinterpret_cast<const uint4*>(p.partial) +
-                             (size_t(next_region) * 64 + (c >> 2)) * 32 + lane;
-          uint4 q[CHUNK / 4];
-#pragma unroll
-          for (int u = 0; u < CHUNK / 4; ++u)
-            q[u] = (4 * u < width) ? __ldcg(src + u * 32) : make_uint4(0u, 0u, 0u, 0u);
-          if (p.acc_int) {
+          // Partial sums of every cluster that shares this tile.  All loads of
+          // a chunk are requested before any is used, so the L2 round trips
+          // overlap instead of queueing behind one another.
+          if (c == 0) {
+            last_sharer = work.last_sharer(w);
+            bool all_here = true;
+            for (int j = cluster_id + 1; j <= last_sharer && all_here; ++j)
+              if (work.has_work(j))
+                all_here = wait_flag(p.flags + my_region + (j - cluster_id) * CTA_GROUP * 4, p.epoch, ctx);
+            if (!all_here) break;
+          }
+          for (int j = cluster_id + 1; j <= last_sharer; ++j) {
+            if (!work.has_work(j)) continue;
+            const uint4* src = reinterpret_cast<const uint4*>(p.partial) +
+                               (size_t(my_region + (j - cluster_id) * CTA_GROUP * 4) * 64 + (c >> 2)) * 32 + lane;
+            uint4 q[CHUNK / 4];
 #pragma unroll
             for (int u = 0; u < CHUNK / 4; ++u)
-              v[4 * u] += q[u].x, v[4 * u + 1] += q[u].y, v[4 * u + 2] += q[u].z, v[4 * u + 3] += q[u].w;
-          } else {
+              q[u] = (4 * u < width) ? __ldcg(src + u * 32) : make_uint4(0u, 0u, 0u, 0u);
+            if (p.acc_int) {
 #pragma unroll
-            for (int u = 0; u < CHUNK / 4; ++u) {
-              v[4 * u] = __float_as_uint(__uint_as_float(v[4 * u]) + __uint_as_float(q[u].x));
-              v[4 * u + 1] = __float_as_uint(__uint_as_float(v[4 * u + 1]) + __uint_as_float(q[u].y));
-              v[4 * u + 2] = __float_as_uint(__uint_as_float(v[4 * u + 2]) + __uint_as_float(q[u].z));
-              v[4 * u + 3] = __float_as_uint(__uint_as_float(v[4 * u + 3]) + __uint_as_float(q[u].w));
+              for (int u = 0; u < CHUNK / 4; ++u)
+                v[4 * u] += q[u].x, v[4 * u + 1] += q[u].y, v[4 * u + 2] += q[u].z, v[4 * u + 3] += q[u].w;
+            } else {
+#pragma unroll
+              for (int u = 0; u < CHUNK / 4; ++u) {
+                v[4 * u] = __float_as_uint(__uint_as_float(v[4 * u]) + __uint_as_float(q[u].x));
+                v[4 * u + 1] = __float_as_uint(__uint_as_float(v[4 * u + 1]) + __uint_as_float(q[u].y));
+                v[4 * u + 2] = __float_as_uint(__uint_as_float(v[4 * u + 2]) + __uint_as_float(q[u].z));
+                v[4 * u + 3] = __float_as_uint(__uint_as_float(v[4 * u + 3]) + __uint_as_float(q[u].w));
+              }
             }
           }
         }

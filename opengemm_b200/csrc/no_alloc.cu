@@ -274,6 +274,7 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
       if ((tag & 0x7FFFFFFFu) == 0) tag = ++dev->calls;
     }
     params.stream_k = 1;
+    params.sk_clusters = clusters;
     params.epoch = int(tag & 0x7FFFFFFFu);
     params.acc_int = p.format->out == OUT_S32;
     params.partial = reinterpret_cast<float*>(dev->workspace);

@@ -102,6 +102,32 @@ def test_stream_k_schedule(name, variant):
         assert_parity(case, got, want=want)
 
 
+@pytest.mark.parametrize(
+    "name,shape,knobs",
+    [
+        ("bf16", (256, 256, 4096), dict(use_2cta=False, output_n=128)),       # 4 tiles, each cut ~37 ways
+        ("s8", (300, 520, 4096), dict(use_2cta=True, output_n=256)),          # 6 ragged tiles over 74 pairs
+        ("mxfp4", (64, 7168, 8192), dict(use_2cta=False, output_n=64, swap_ab=True)),   # decode shard: 56 tiles, 148 CTAs
+        ("nvfp4", (64, 3072, 2048), dict(use_2cta=False, output_n=64, swap_ab=True)),
+        ("mxfp4", (64, 57344, 1024), dict(use_2cta=False, output_n=64, swap_ab=True)),  # 3 whole waves + 4 tiles cut along K
+        ("e4m3", (1, 8192, 8192), dict(use_2cta=False, output_n=16, swap_ab=True)),
+    ],
+)
+def test_stream_k_many_way_split(name, shape, knobs):
+    """With fewer tiles than clusters (or a small remainder wave) a tile is cut
+    along K across many clusters and finished by the one holding its first blocks."""
+    from opengemm_b200 import capi
+
+    m, n, k = shape
+    config = _config(name, split_k=2, **knobs)
+    lib, g = capi.bind(name, m, n, k, config)
+    plan = lib.plan(g, 0)
+    assert plan["stream_k"] == 1 and plan["grid"] == 148
+    case = make_case(name, m, n, k, seed=8)
+    for _ in range(2):
+        assert_parity(case, run_library(case, config))
+
+
 @pytest.mark.parametrize("name", ["bf16", "s8", "nvfp4"])
 def test_dense_rows_of_ones_known_answer(name):
     """A known-answer case no tolerance is needed for: all-ones operands give K everywhere."""
