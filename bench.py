@@ -44,6 +44,10 @@ WORKLOADS = {
            "what": "nvfp4 block-scaled GEMM 8192x28672x8192 -> bf16, N(0,1), scale = amax/6 as ue4m3 per 16"},
     "c5": {"name": "mxfp4", "m": 64, "n": 57344, "k": 8192,
            "what": "mxfp4 block-scaled decode GEMM 64x57344x8192 -> bf16, N(0,1), scale = 2^floor(log2(amax/6)) per 32"},
+    # the per-GPU shards of c3 / c4 / c5 when N is split over eight GPUs
+    "c3s": {"name": "s8", "m": 8192, "n": 1024, "k": 8192, "what": "s8 GEMM 8192x1024x8192 (one eighth of c3's N)"},
+    "c4s": {"name": "nvfp4", "m": 8192, "n": 3584, "k": 8192, "what": "nvfp4 GEMM 8192x3584x8192 (one eighth of c4's N)"},
+    "c5s": {"name": "mxfp4", "m": 64, "n": 7168, "k": 8192, "what": "mxfp4 decode GEMM 64x7168x8192 (one eighth of c5's N)"},
 }
 L2_BYTES = 126 * 2**20
 # Dense tensor-core peaks by format relative to bf16 (nominal bf16 2250 TFLOP/s):
@@ -52,8 +56,8 @@ RATE_VS_BF16 = {"bf16": 1.0, "e4m3": 2.0, "e4m3xe5m2": 2.0, "s8": 2.0, "nvfp4": 
 NOMINAL_BF16_TFLOPS = 2250.0
 # dram bytes (read + write) of one launch of the dominant kernel in this
 # benchmark's own rotation of buffers, from the ncu captures summarised under
-# profiles/ (gemm_kernel_<workload>.md); None where no capture is committed.
-NCU_TRAFFIC_BYTES = {"c2": 53.7e6}
+# profiles/; None where no capture is committed.
+NCU_TRAFFIC_BYTES = {"c2": 53.7e6, "c5": 256.2e6, "c4s": 94.7e6, "c1": 4.2e6, "c3s": 80.9e6}
 
 
 def measured_peaks():
@@ -428,30 +432,67 @@ def run_ours(args):
     per_gpu = (r.per_set / kernel_us / 1e3) if unit == "GB/s" else (flops_step / kernel_us / 1e6)
     value = per_gpu * world
 
-    # End to end through the public API, every step fed from pinned host memory.
+    # End to end through the public API, every step fed from pinned host memory:
+    # host->device copies of the step's operands, gemm(), device->host copy of
+    # the result.  Three streams and two sets of buffers let step i+1's upload
+    # run under step i's download (the link is full duplex); every step still
+    # performs all three, in order, on its own buffers.
     a0, b0, sfa0, sfb0, _ = r.sets[0]
     host_in = [t.cpu().pin_memory() for t in (a0, b0, sfa0, sfb0) if t is not None]
-    dev_in = [torch.empty_like(t) for t in (a0, b0, sfa0, sfb0) if t is not None]
-    dev_c = torch.empty((m, n), device=device, dtype=r.d.out)
-    host_c = torch.empty((m, n), dtype=r.d.out).pin_memory()
-    e2e_steps = max(3, min(args.steps, 30))
+    lanes = []
+    for _ in range(2):
+        lanes.append({
+            "dev_in": [torch.empty_like(t) for t in (a0, b0, sfa0, sfb0) if t is not None],
+            "dev_c": torch.empty((m, n), device=device, dtype=r.d.out),
+            "host_c": torch.empty((m, n), dtype=r.d.out).pin_memory(),
+            "uploaded": torch.cuda.Event(), "computed": torch.cuda.Event(), "downloaded": torch.cuda.Event(),
+        })
+    up, compute, down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    e2e_steps = max(4, min(args.steps, 40))
+    state = {"i": 0}
 
     def e2e_step():
-        for dst, src in zip(dev_in, host_in):
-            dst.copy_(src, non_blocking=True)
-        og.gemm(*dev_in, out=dev_c)
-        host_c.copy_(dev_c, non_blocking=True)
+        lane = lanes[state["i"] % 2]
+        state["i"] += 1
+        with torch.cuda.stream(up):
+            up.wait_event(lane["computed"])  # the lane's previous GEMM has read its operands
+            for dst, src in zip(lane["dev_in"], host_in):
+                dst.copy_(src, non_blocking=True)
+            lane["uploaded"].record(up)
+        with torch.cuda.stream(compute):
+            compute.wait_event(lane["uploaded"])
+            compute.wait_event(lane["downloaded"])  # the lane's previous result has left dev_c
+            og.gemm(*lane["dev_in"], out=lane["dev_c"])
+            lane["computed"].record(compute)
+        with torch.cuda.stream(down):
+            down.wait_event(lane["computed"])
+            lane["host_c"].copy_(lane["dev_c"], non_blocking=True)
+            lane["downloaded"].record(down)
 
-    for _ in range(3):
-        e2e_step()
+    def e2e_run(steps):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        current = torch.cuda.current_stream()
+        for s in (up, compute, down):
+            s.wait_stream(current)
+        start.record(up)
+        for _ in range(steps):
+            e2e_step()
+        current.wait_stream(down)
+        current.wait_stream(compute)
+        current.wait_stream(up)
+        end.record(current)
+        end.synchronize()
+        return start.elapsed_time(end)
+
+    e2e_run(4)
     barrier()
-    e2e_ms = time_launches(torch, e2e_step, e2e_steps)
+    e2e_ms = e2e_run(e2e_steps)
     barrier()
     e2e_ms = max_over_ranks(e2e_ms)
     e2e_us = e2e_ms * 1e3 / e2e_steps
     e2e_value = world * ((r.per_set / e2e_us / 1e3) if unit == "GB/s" else (flops_step / e2e_us / 1e6))
     h2d = sum(t.numel() * t.element_size() for t in host_in)
-    d2h = host_c.numel() * host_c.element_size()
+    d2h = lanes[0]["host_c"].numel() * lanes[0]["host_c"].element_size()
 
     if rank != 0:
         if world > 1:

@@ -167,8 +167,12 @@ int follow_device(int device) {
   return OG_OK;
 }
 
+std::atomic<int> sm_count_fast[64];
+std::atomic<uint64_t> configured_fast[64];
+
 int sm_count_of(int device) {
   if (device < 0) return 148;
+  if (const int known = sm_count_fast[device & 63].load(std::memory_order_relaxed)) return known;
   std::lock_guard<std::mutex> lock(device_mutex);
   DeviceInfo& info = devices[device & 63];
   if (!info.sm_count) {
@@ -177,19 +181,22 @@ int sm_count_of(int device) {
       count = 148;
     info.sm_count = count;
   }
+  sm_count_fast[device & 63].store(info.sm_count, std::memory_order_relaxed);
   return info.sm_count;
 }
 
 int ensure_configured(int device, int variant, int smem_bytes) {
+  const uint64_t bit = 1ull << variant;
+  if (configured_fast[device & 63].load(std::memory_order_acquire) & bit) return OG_OK;
   std::lock_guard<std::mutex> lock(device_mutex);
   DeviceInfo& info = devices[device & 63];
-  const uint64_t bit = 1ull << variant;
   if (info.configured & bit) return OG_OK;
   const cudaError_t status = configure_variant(variant, SMEM_LIMIT - 1024);  // static barriers take the rest
   if (status != cudaSuccess)
     return fail(OG_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(status));
   (void)smem_bytes;
   info.configured |= bit;
+  configured_fast[device & 63].fetch_or(bit, std::memory_order_release);
   return OG_OK;
 }
 
@@ -252,13 +259,27 @@ int bind_impl(OgGemm* g, bool scaled) {
   return OG_OK;
 }
 
+// The plan of the OgGemm this thread launched last: launches of one bound
+// GEMM in a loop skip re-deriving it.
+struct PlanMemo {
+  OgGemm key;
+  Plan plan;
+  bool valid = false;
+};
+thread_local PlanMemo plan_memo;
+
 int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, const void* sfb,
                 void* c, int device, void* stream, int* status_word, int want_scaled) {
   if (!g) return fail(OG_ERR_LAUNCH, "null OgGemm");
-  Plan p;
-  char why[256];
-  const int planned = make_plan(*g, 148, &p, why, sizeof why);
-  if (planned != OG_OK) return fail(planned, "%s", why);
+  if (!plan_memo.valid || std::memcmp(&plan_memo.key, g, sizeof(OgGemm)) != 0) {
+    char why[256];
+    plan_memo.valid = false;
+    const int planned = make_plan(*g, 148, &plan_memo.plan, why, sizeof why);
+    if (planned != OG_OK) return fail(planned, "%s", why);
+    plan_memo.key = *g;
+    plan_memo.valid = true;
+  }
+  const Plan& p = plan_memo.plan;
   if (g->row != p.variant)
     return fail(OG_ERR_LAUNCH, "row %d is not the kernel of this OgGemm: bind it first", g->row);
   if (want_scaled >= 0 && int(p.format->scaled) != want_scaled)
