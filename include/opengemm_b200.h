@@ -104,7 +104,8 @@ typedef struct {
   int32_t tmem_cols, smem_bytes;
   int32_t tiles, grid; /* output tiles; CTAs launched */
   int32_t group;     /* rasterisation band width in tiles */
-  int32_t stream_k;  /* K blocks dealt out in equal ranges across tiles (split_k >= 2) */
+  int32_t stream_k;  /* partial wave cut along K across clusters (split_k >= 2) */
+  int32_t use_clc;   /* tiles handed out by cluster launch control; grid = one cluster per tile */
 } OgPlan;
 
 /* Describe how `g` (already bound by og_mm_bind / og_smm_bind) would run on `device`
@@ -122,6 +123,19 @@ OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void
  * object of integers written to `out` (what the standalone-kernel emitter bakes
  * into the code it writes).  Needs no GPU. */
 OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, int32_t cap);
+
+/* Block-scaled quantisation on the GPU, the step upstream of every block-scaled GEMM:
+ * `x` ([rows, k] bfloat16, or float32 when x_is_f32) -> `packed` (the operand in the
+ * format's storage: k/2 bytes per row for nvfp4 / mxfp4, k for mxfp8), `scales`
+ * ([rows, k/block] bytes, row-major; may be null) and `scales_blocked` (the 128x4
+ * blocked layout og_smm_launch reads, ceil(rows/128)*128 x ceil(k/(4*block))*4 bytes;
+ * may be null).  Same arithmetic, bit for bit, as the reference's torch helper
+ * (opengemm/python/quant.py:99-122 followed by to_blocked, quant.py:82-97), in one
+ * pass.  `format` is "nvfp4", "mxfp8" or "mxfp4".  Errors: og_b200_quantize_error(). */
+OG_API int32_t og_b200_quantize(const char* format, const void* x, int32_t x_is_f32, int64_t rows,
+                                int64_t k, void* packed, void* scales, void* scales_blocked,
+                                int32_t device, void* stream);
+OG_API const char* og_b200_quantize_error(void);
 
 /* Limit of every device-side wait in milliseconds (default 2000). */
 OG_API void og_b200_set_wait_limit_ms(int32_t ms);

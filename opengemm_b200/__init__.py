@@ -13,7 +13,7 @@ from .api import gemm
 from .build import prebuild
 from .dtypes import DTYPES, dtype_name
 from .emit import emit_kernel
-from .quant import pack, quantize, to_blocked, unpack
+from .quant import pack, quantize, quantize_blocked, to_blocked, unpack
 from .run import run_kernel
 
 __all__ = [

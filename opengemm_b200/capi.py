@@ -51,7 +51,7 @@ class OgPlan(ctypes.Structure):
         (f, c_int32)
         for f in (
             "cta_group", "tile_m", "tile_n", "block_k", "stages", "swap", "epi_tma",
-            "acc_slots", "tmem_cols", "smem_bytes", "tiles", "grid", "group", "stream_k",
+            "acc_slots", "tmem_cols", "smem_bytes", "tiles", "grid", "group", "stream_k", "use_clc",
         )
     ]
 
@@ -133,6 +133,12 @@ class Library:
             self._checked.argtypes = [POINTER(OgGemm)] + [c_void_p] * 5 + [c_int32, c_void_p, c_void_p]
             self._set_limit = lib.og_b200_set_wait_limit_ms
             self._set_limit.restype, self._set_limit.argtypes = None, [c_int32]
+            self._quantize = lib.og_b200_quantize
+            self._quantize.restype = c_int32
+            self._quantize.argtypes = [c_char_p, c_void_p, c_int32, ctypes.c_int64, ctypes.c_int64, c_void_p, c_void_p,
+                                       c_void_p, c_int32, c_void_p]
+            self._quantize_error = lib.og_b200_quantize_error
+            self._quantize_error.restype = c_char_p
             self._describe = lib.og_b200_describe
             self._describe.restype = c_int32
             self._describe.argtypes = [POINTER(OgGemm), c_int32, c_char_p, c_int32]
@@ -211,6 +217,17 @@ class Library:
         if self._describe(byref(g), sm_count, text, len(text)) != OG_OK:
             raise RuntimeError(self.error())
         return json.loads(text.value.decode())
+
+    def quantize(self, name, x, packed, scales, blocked):
+        """Run the quantisation kernel on CUDA tensors (`scales` / `blocked` may be None)."""
+        device = x.get_device()
+        status = self._quantize(
+            name.encode(), x.data_ptr(), int(x.dtype is torch.float32), x.size(0), x.size(1), packed.data_ptr(),
+            0 if scales is None else scales.data_ptr(), 0 if blocked is None else blocked.data_ptr(),
+            device, raw_stream(device),
+        )
+        if status != OG_OK:
+            raise RuntimeError(self._quantize_error().decode())
 
     def set_wait_limit_ms(self, ms):
         self._set_limit(int(ms))

@@ -365,6 +365,12 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
 
   const int sm_count = sm_count_of(device);
   int grid = grid_for(p, sm_count);
+  if (g->use_clc && g->split_k < 2) {
+    // Cluster launch control: one cluster per tile; running clusters take over
+    // the tiles of those that have not started.
+    params.use_clc = 1;
+    grid = p.num_tiles * p.cta_group;
+  }
   if (g->split_k >= 2 && use_stream_k(*g, p, grid_for(p, sm_count, true))) {
     grid = grid_for(p, sm_count, true);
     unsigned epoch = ++launch_epoch;
@@ -464,6 +470,11 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
   out->tiles = p.num_tiles;
   out->grid = grid_for(p, sm_count_of(device));
   out->group = p.group;
+  out->use_clc = 0;
+  if (g->use_clc && g->split_k < 2) {
+    out->use_clc = 1;
+    out->grid = p.num_tiles * p.cta_group;
+  }
   out->stream_k = 0;
   if (g->split_k >= 2 && use_stream_k(*g, p, grid_for(p, sm_count_of(device), true))) {
     out->grid = grid_for(p, sm_count_of(device), true);

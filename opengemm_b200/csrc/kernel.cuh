@@ -29,6 +29,8 @@ constexpr int MAX_STAGES = 16;
 constexpr int THREADS = 192;
 constexpr int SWIZZLE_ALIGN = 1024;
 constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows of one 128-byte swizzle row
+constexpr int CLC_SLOTS = 3;             // answers in flight between the fastest and the slowest role
+constexpr int CLC_READERS = 6;           // per CTA: producer, warp 1's thread, four epilogue warps
 
 struct alignas(64) GemmParams {
   CUtensorMap map_x;    // MMA-M side operand, [rows_m, K]
@@ -62,6 +64,7 @@ struct alignas(64) GemmParams {
   int pdl;                // wait for the previous grid before touching memory
   // Stream-K: the (tile, K-block) units are dealt out in equal contiguous
   // ranges, so a range may begin or end inside a tile.  See WorkIter.
+  int use_clc;            // tiles come from cluster launch control instead of a fixed stride
   int stream_k;
   int sk_clusters;        // clusters that share the partial wave's units (the rest only run whole tiles)
   int acc_int;            // accumulators are s32 (partials add as integers)
@@ -105,10 +108,27 @@ struct Work {
 // f32/s32 partial sums in its own workspace region and never waits, so the
 // schedule cannot deadlock while all clusters are resident.  A range starts
 // inside at most one tile, so a cluster contributes at most once per launch.
+//
+// Cluster launch control (use_clc): the grid has one cluster per tile; a
+// running cluster takes over the tile of a cluster that has not started yet.
+// The pair leader's producer thread asks for one at the start of every tile
+// (clc_request); every role reads the answer when it finishes the tile
+// (inside next).  In a pair the leader forwards the answer to its peer through
+// distributed shared memory; nothing is multicast.
+struct ClcState {
+  uint32_t full, empty_leader, answers;  // barrier arrays and answer slots (shared-memory addresses)
+  uint32_t rank;
+  bool forwards;                          // this thread is the leader's producer
+  bool arrives;                           // this thread reports having read an answer
+  const WaitCtx* ctx;
+};
+
 struct WorkIter {
   int stream_k, k_blocks, clusters, cluster, step;
   int tile, static_tiles;
   long long total, u, u_end;
+  int use_clc, cta_group, answered;
+  ClcState clc;
   // `clusters` below is the number of clusters that share the partial wave
   // (p.sk_clusters, at most the grid's); `step` is the grid's cluster count.
   __device__ __forceinline__ WorkIter(const GemmParams& p, int cluster_, int grid_clusters) {
@@ -123,8 +143,54 @@ struct WorkIter {
     const bool shares = cluster_ < clusters;
     u = shares ? total * cluster_ / clusters : 0;
     u_end = shares ? total * (cluster_ + 1) / clusters : 0;
+    use_clc = 0;
+    answered = -1;
+  }
+  __device__ __forceinline__ void enable_clc(const ClcState& state, int cta_group_) {
+    use_clc = 1;
+    cta_group = cta_group_;
+    clc = state;
+  }
+  // Leader's producer, at the start of the tile it is about to load: ask for
+  // the tile after it.  `answered` answers have been consumed so far, so
+  // this is request number `answered`.
+  __device__ __forceinline__ bool clc_request() {
+    const int n = answered;
+    const int slot = n % CLC_SLOTS;
+    const uint32_t phase = (n / CLC_SLOTS) & 1;
+    if (!mbar_wait(clc.empty_leader + 8 * slot, phase ^ 1, *clc.ctx, SITE_CLC)) return false;
+    mbar_expect_tx(clc.full + 8 * slot, 16);
+    clc_try_cancel(clc.answers + 16 * slot, clc.full + 8 * slot);
+    return true;
+  }
+  __device__ __forceinline__ bool next_clc(Work& w) {
+    if (answered < 0) {  // the tile this cluster was launched for
+      answered = 0;
+      w = {cluster, 0, k_blocks};
+      return true;
+    }
+    const int n = answered;
+    const int slot = n % CLC_SLOTS;
+    const uint32_t phase = (n / CLC_SLOTS) & 1;
+    if (!mbar_wait(clc.full + 8 * slot, phase, *clc.ctx, SITE_CLC)) return false;
+    const uint4 answer = ld_shared_v4(clc.answers + 16 * slot);
+    if (clc.forwards && cta_group == 2) {
+      st_cluster_v4(map_to_cta(clc.answers + 16 * slot, 1), answer);
+      mbar_arrive_cluster(map_to_cta(clc.full + 8 * slot, 1));
+    }
+    fence_async_smem();  // the slot's next answer arrives through the async proxy
+    if (clc.arrives) {
+      if (cta_group == 2) mbar_arrive_cluster(clc.empty_leader + 8 * slot);
+      else mbar_arrive(clc.empty_leader + 8 * slot);
+    }
+    answered = n + 1;
+    const int first_cta = clc_decode(answer);
+    if (first_cta < 0) return false;
+    w = {first_cta / cta_group, 0, k_blocks};
+    return true;
   }
   __device__ __forceinline__ bool next(Work& w) {
+    if (use_clc) return next_clc(w);
     if (tile < static_tiles) {
       w = {tile, 0, k_blocks};
       tile += step;
@@ -170,7 +236,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   constexpr int TILE_M = 128 * CTA_GROUP;
 
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4 + 2 * CLC_SLOTS];
+  __shared__ __align__(16) uint4 clc_answers[CLC_SLOTS];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -186,6 +253,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   const uint32_t bar_empty = bar_full + 8 * MAX_STAGES;
   const uint32_t bar_acc_full = bar_empty + 8 * MAX_STAGES;
   const uint32_t bar_acc_empty = bar_acc_full + 16;
+  const uint32_t bar_clc_full = bar_acc_empty + 16;
+  const uint32_t bar_clc_empty = bar_clc_full + 8 * CLC_SLOTS;
 
   const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
 
@@ -197,6 +266,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_acc_full + 8 * s, 1);
       mbar_init(bar_acc_empty + 8 * s, 4 * CTA_GROUP);
+    }
+    if (p.use_clc) {
+      for (int s = 0; s < CLC_SLOTS; ++s) {
+        mbar_init(bar_clc_full + 8 * s, 1);  // leader: the answer's 16 bytes; peer: the leader's forward
+        mbar_init(bar_clc_empty + 8 * s, CLC_READERS * CTA_GROUP);
+      }
     }
     abort_flag = 0;
     mbar_init_fence();
@@ -221,6 +296,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   // may start its own set-up on SMs this grid leaves free.  Every thread of
   // this grid that touches global memory first waits for the previous grid.
   if (p.pdl && threadIdx.x == 0) pdl_launch_dependents();
+  const uint32_t clc_empty_leader = (CTA_GROUP == 2) ? map_to_cta(bar_clc_empty, 0) : bar_clc_empty;
+  auto clc_state = [&](bool forwards, bool arrives) {
+    return ClcState{bar_clc_full, clc_empty_leader, smem_u32(clc_answers), rank, forwards, arrives, &ctx};
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -238,8 +317,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       uint32_t issued = 0;
       bool ok = true;
       WorkIter work(p, cluster_id, num_clusters);
+      if (p.use_clc) work.enable_clc(clc_state(rank == 0, true), CTA_GROUP);
       Work w;
       while (ok && work.next(w)) {
+        if (p.use_clc && rank == 0 && !work.clc_request()) break;
         const TileCoord t = tile_coord(p, w.tile);
         const int row_x = t.mi * TILE_M + int(rank) * 128;
         const int row_y = t.ni * p.tile_n + int(rank) * y_rows;
@@ -290,7 +371,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     // ---------------------------------------------------------- MMA issuer
     // One thread of the pair's leader.  Descriptors advance by addition; the
     // scale copies and the four MMAs of a stage are fully unrolled.
-    if (rank == 0 && elect_one()) {
+    if (rank != 0) {
+      if (p.use_clc && elect_one()) {  // the peer's idle warp still reads every answer
+        WorkIter work(p, cluster_id, num_clusters);
+        work.enable_clc(clc_state(false, true), CTA_GROUP);
+        Work w;
+        while (work.next(w)) {
+        }
+      }
+    } else if (elect_one()) {
       constexpr int SF_ATOMS = KIND == KIND_NVF4 ? 4 : KIND == KIND_MXF4 ? 2 : 1;
       const uint64_t desc_stage = uint64_t(p.stage_bytes >> 4);
       const uint64_t dx0 = operand_desc(ring);
@@ -305,6 +394,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       int tile_idx = 0;
       bool ok = true;
       WorkIter work(p, cluster_id, num_clusters);
+      if (p.use_clc) work.enable_clc(clc_state(false, true), CTA_GROUP);
       Work w;
       for (; ok && work.next(w); ++tile_idx) {
         const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
@@ -384,6 +474,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     const int my_region = (cluster_id * CTA_GROUP + int(rank)) * 4 + quarter;
     int last_sharer = 0;  // last cluster after this one that shares the tile being finished
     WorkIter work(p, cluster_id, num_clusters);
+    if (p.use_clc) work.enable_clc(clc_state(false, lane == 0), CTA_GROUP);
     Work w;
     for (; work.next(w); ++tile_idx) {
       const TileCoord t = tile_coord(p, w.tile);

@@ -36,6 +36,7 @@ enum WaitSite : int {
   SITE_EPI_ACC_FULL = 4,
   SITE_DRAIN = 5,
   SITE_PARTIAL_FLAG = 6,
+  SITE_CLC = 7,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -232,6 +233,47 @@ __device__ __forceinline__ void pdl_wait_prior_grids() {
 
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---- cluster launch control ----------------------------------------------------
+
+// Ask the hardware to cancel a cluster of this grid that has not started yet.
+// The 16-byte answer lands in this CTA's shared memory at `response` and
+// completes 16 bytes on `bar` (no fan-out to other CTAs).
+__device__ __forceinline__ void clc_try_cancel(uint32_t response, uint32_t bar) {
+  asm volatile(
+      "clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];" ::"r"(
+          response),
+      "r"(bar)
+      : "memory");
+}
+
+// Decode an answer: the first CTA id (x) of the cancelled cluster, or -1 when
+// nothing was left to cancel.
+__device__ __forceinline__ int clc_decode(uint4 answer) {
+  uint32_t ok, x;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b128 h;\n\t"
+      "mov.b128 h, {%2, %3, %4, %5};\n\t"
+      "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, h;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "mov.u32 %1, 0;\n\t"
+      "@p clusterlaunchcontrol.query_cancel.get_first_ctaid::x.b32.b128 %1, h;\n\t}"
+      : "=r"(ok), "=r"(x)
+      : "r"(answer.x), "r"(answer.y), "r"(answer.z), "r"(answer.w));
+  return ok ? int(x) : -1;
+}
+
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// Store 16 bytes into another CTA's shared memory (`addr` from map_to_cta).
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
 
 // ---- tensor memory ------------------------------------------------------------

@@ -111,6 +111,46 @@ def to_blocked(scales):
     return atoms.reshape(-1).contiguous()
 
 
+def _scale_buffers(d, rows, k, device, raw, blocked):
+    block = sf_block(d)
+    raw_t = torch.empty((rows, k // block), dtype=torch.uint8, device=device) if raw else None
+    blocked_t = None
+    if blocked:
+        nbytes = (-(-rows // 128) * 128) * (-(-k // (block * 4)) * 4)
+        blocked_t = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    return raw_t, blocked_t
+
+
+def _quantize_cuda(x, name, raw, blocked):
+    """The CUDA path: one kernel writes the packed operand and the scales."""
+    from . import capi
+
+    d = DTYPES[name]
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        x = x.float()
+    x = x.contiguous()
+    rows, k = x.shape
+    packed = torch.empty((rows, k * d.bits // 8), dtype=torch.uint8, device=x.device)
+    raw_t, blocked_t = _scale_buffers(d, rows, k, x.device, raw, blocked)
+    capi.library("smm").quantize(name, x, packed, raw_t, blocked_t)
+    return (packed.view(d.a), None if raw_t is None else raw_t.view(d.sf),
+            None if blocked_t is None else blocked_t.view(d.sf))
+
+
+def quantize_blocked(x, name):
+    """Quantise and lay the scales out for `gemm` in one step.
+
+    Returns:
+        `(packed, blocked_scales)`: what `gemm(a, b, sfa, sfb)` takes.  On a CUDA
+        tensor this is a single kernel; on the CPU it is `quantize` + `to_blocked`.
+    """
+    if x.is_cuda:
+        packed, _, blocked = _quantize_cuda(x, name, raw=False, blocked=True)
+        return packed, blocked
+    packed, scales = quantize(x, name)
+    return packed, to_blocked(scales)
+
+
 def quantize(x, name):
     """Quantise `(rows, K)` values to a block-scaled format.
 
@@ -120,8 +160,13 @@ def quantize(x, name):
 
     Returns:
         `(packed, scales)`: the operand in the format's torch dtype and the
-        `(rows, K / block)` scales in the scale dtype, not yet blocked.
+        `(rows, K / block)` scales in the scale dtype, not yet blocked.  CUDA
+        tensors go through the library's quantisation kernel, CPU tensors
+        through the torch arithmetic below; both give the same bytes.
     """
+    if x.is_cuda:
+        packed, scales, _ = _quantize_cuda(x, name, raw=True, blocked=False)
+        return packed, scales
     d = DTYPES[name]
     elem = elems(name)[0]
     block = sf_block(d)

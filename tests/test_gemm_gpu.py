@@ -129,6 +129,25 @@ def test_stream_k_many_way_split(name, shape, knobs):
 
 
 @pytest.mark.parametrize("name", ["bf16", "s8", "nvfp4"])
+@pytest.mark.parametrize("two", [False, True], ids=["single", "pair"])
+@pytest.mark.parametrize("shape", [(520, 712, 1152), (4096, 4096, 512), (3000, 2100, 128)], ids=lambda s: "x".join(map(str, s)))
+def test_cluster_launch_control_scheduler(name, two, shape):
+    """use_clc: one cluster per tile, running clusters take over the tiles of
+    clusters that have not started; the product must not change.  The shapes
+    cover fewer tiles than SMs, many more tiles than SMs, and very short K
+    loops (the producer runs several tiles ahead of the epilogue)."""
+    from opengemm_b200 import capi
+
+    m, n, k = shape
+    config = _config(name, use_2cta=two, output_n=128, use_clc=True)
+    lib, g = capi.bind(name, m, n, k, config)
+    plan = lib.plan(g, 0)
+    assert plan["use_clc"] == 1 and plan["grid"] == plan["tiles"] * plan["cta_group"]
+    case = make_case(name, m, n, k, seed=9)
+    assert_parity(case, run_library(case, config))
+
+
+@pytest.mark.parametrize("name", ["bf16", "s8", "nvfp4"])
 def test_dense_rows_of_ones_known_answer(name):
     """A known-answer case no tolerance is needed for: all-ones operands give K everywhere."""
     m, n, k = 192, 320, 256
