@@ -66,6 +66,21 @@ __device__ __forceinline__ float from_e4m3(uint32_t code) {
 // scan leaves it.
 __device__ __forceinline__ uint32_t to_e2m1(float x) {
   const float a = fabsf(x);
+  if (!(a < 64.0f)) {
+    // Far outside the format (the block's scale underflowed): float32 can no
+    // longer tell the distances to the sixteen values apart, and the
+    // reference's scan - keep the first best, move to an even code only from
+    // an odd one on an exact tie - decides.  Repeat that scan literally.
+    const float values[16] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+    uint32_t code = 0;
+    float best = fabsf(__fsub_rn(x, values[0]));
+#pragma unroll
+    for (uint32_t c = 1; c < 16; ++c) {
+      const float d = fabsf(__fsub_rn(x, values[c]));
+      if (d < best || (d == best && (c & 1) == 0 && (code & 1) == 1)) best = d, code = c;
+    }
+    return code;
+  }
   uint32_t code = 0;
   code += a > 0.25f;   // tie at .25 stays at code 0 (even)
   code += a >= 0.75f;  // tie at .75 goes up to code 2 (even)
@@ -134,6 +149,10 @@ __global__ void __launch_bounds__(128) quantize_kernel(const void* __restrict__ 
         stored_value = __uint_as_float(stored << 23);
       }
       const float divisor = fmaxf(stored_value, 1e-30f);
+      // A ue4m3 scale past the format's range is stored as NaN; dividing by it
+      // makes every value NaN, which the reference's nearest-code scan leaves
+      // at code 0.
+      const bool nan_scale = FORMAT == Q_NVFP4 && (stored & 0x7Fu) == 0x7Fu;
       scale_word |= stored << (8 * j);
       if (scales) scales[row * k_blocks + kb] = uint8_t(stored);
       // quantise through bfloat16, as the reference does
@@ -147,7 +166,7 @@ __global__ void __launch_bounds__(128) quantize_kernel(const void* __restrict__ 
             const float q = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(v[8 * i + h], divisor)));
             w |= to_e2m1(q) << (4 * h);
           }
-          words[i] = w;
+          words[i] = nan_scale ? 0u : w;
         }
         uint8_t* dst = packed + (row * k + kb * BLOCK) / 2;
         if constexpr (BLOCK == 16) {
