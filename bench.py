@@ -347,6 +347,30 @@ def side_configs(torch, device, skip):
             torch.cuda.empty_cache()
         except Exception as exc:  # a side measurement must never cost the headline
             results[key] = {"error": str(exc)[:160]}
+    # The quantisation kernel upstream of the block-scaled GEMMs: bf16 values in,
+    # packed nvfp4 + blocked ue4m3 scales out, on c4's B operand shape.
+    try:
+        import opengemm_b200 as og
+
+        rows, k = 28672, 8192
+        xs = [torch.randn((rows, k), device=device).to(torch.bfloat16) for _ in range(2)]
+        state = {"i": 0}
+
+        def quantize_step():
+            state["i"] += 1
+            og.quantize_blocked(xs[state["i"] % 2], "nvfp4")
+
+        for _ in range(3):
+            quantize_step()
+        torch.cuda.synchronize()
+        us = min(time_launches(torch, quantize_step, 10) for _ in range(3)) * 1e3 / 10
+        nbytes = rows * k * 2 + rows * k // 2 + rows * k // 16
+        results["quantize_nvfp4_28672x8192"] = {"us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1),
+                                                "algorithmic_bytes": nbytes}
+        del xs
+        torch.cuda.empty_cache()
+    except Exception as exc:
+        results["quantize_nvfp4_28672x8192"] = {"error": str(exc)[:160]}
     return results
 
 

@@ -14,9 +14,11 @@
 // One thread owns four consecutive scale blocks of one row (64 values for
 // nvfp4, 128 for the mx formats): it reads them with 16-byte loads, writes
 // 32-128 contiguous bytes of packed output and one 32-bit word of four scales.
-// A CTA of 128 threads covers 128 rows, so its scale words make up exactly
-// one 512-byte atom of the blocked layout.  HBM-bound: 2 (bf16) or 4 (f32)
-// bytes read and 0.5-1 byte plus 1/16-1/32 byte written per value.
+// Neighbouring lanes own neighbouring groups of the same row, so a warp reads
+// and writes contiguous kilobytes; a CTA covers 128 rows x 8 groups and writes
+// its eight 512-byte atoms of the blocked scale layout whole.  HBM-bound: 2
+// (bf16) or 4 (f32) bytes read and 0.5-1 byte plus 1/16-1/32 byte written per
+// value.
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -92,40 +94,92 @@ __device__ __forceinline__ uint32_t to_e2m1(float x) {
   return (code && x < 0.f) ? (code | 8u) : code;
 }
 
+// Eight float32 values -> eight e2m1 codes in one 32-bit word (value 0 in the
+// low nibble) with the hardware's packed conversion: nearest even, saturating
+// at +-6.  The hardware keeps the sign of a value that rounds to zero; the
+// reference stores +0 there, so sign bits of zero magnitudes are cleared.
+__device__ __forceinline__ uint32_t pack_e2m1x8(const float* q) {
+  uint32_t w = 0;
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    uint32_t byte;
+    asm("{\n\t.reg .b8 t;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t, %2, %1;\n\t"
+        "cvt.u32.u8 %0, t;\n\t}"
+        : "=r"(byte)
+        : "f"(q[2 * h]), "f"(q[2 * h + 1]));
+    w |= byte << (8 * h);
+  }
+  const uint32_t magnitude = w & 0x77777777u;
+  const uint32_t nonzero = ((magnitude + 0x77777777u) | magnitude) & 0x88888888u;
+  return magnitude | (w & nonzero);
+}
+
+// Four float32 values -> four e4m3 codes, nearest even (every quotient of a
+// block is at most 448 in magnitude, so saturation never differs from torch).
+__device__ __forceinline__ uint32_t pack_e4m3x4(const float* q) {
+  uint32_t lo, hi;
+  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}"
+      : "=r"(lo) : "f"(q[0]), "f"(q[1]));
+  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}"
+      : "=r"(hi) : "f"(q[2]), "f"(q[3]));
+  return lo | (hi << 16);
+}
+
+__device__ __forceinline__ float through_bf16(float x) {
+  return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+constexpr int Q_THREADS = 256;
+constexpr int Q_GROUPS = 8;  // K groups (of four scale blocks) per CTA
+
+// A CTA covers 128 rows x 8 K groups.  Eight consecutive lanes read one row's
+// eight groups, 1-2 KiB of contiguous input; the CTA walks the four 32-row
+// quarters of its row block, collects the scale words in shared memory and
+// then writes its eight 512-byte scale atoms whole.
 template <int FORMAT, bool F32_IN>
-__global__ void __launch_bounds__(128) quantize_kernel(const void* __restrict__ x, int64_t rows, int64_t k,
-                                                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
-                                                       uint8_t* __restrict__ blocked) {
+__global__ void __launch_bounds__(Q_THREADS, F32_IN ? 1 : 2) quantize_kernel(const void* __restrict__ x, int64_t rows, int64_t k,
+                                                             uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+                                                             uint8_t* __restrict__ blocked) {
   constexpr int BLOCK = FORMAT == Q_NVFP4 ? 16 : 32;  // values per scale
   constexpr bool FP4 = FORMAT != Q_MXFP8;
   constexpr float TOP = FP4 ? 6.0f : 448.0f;
+  constexpr int VEC = F32_IN ? 4 : 8;                 // values per 16-byte load
+  constexpr int LOADS = BLOCK / VEC;                  // loads per scale block
   const int64_t k_blocks = k / BLOCK;
   const int64_t k_groups = (k_blocks + 3) / 4;
-  const int64_t row = int64_t(blockIdx.y) * 128 + threadIdx.x;
-  const int64_t group = blockIdx.x;  // four scale blocks along K
+  __shared__ uint32_t scale_words[Q_GROUPS][128];
+  const int group_in_cta = threadIdx.x % Q_GROUPS;
+  const int64_t group = int64_t(blockIdx.x) * Q_GROUPS + group_in_cta;  // four scale blocks along K
+#pragma unroll 1
+  for (int quarter = 0; quarter < 4; ++quarter) {
+  const int row_in_block = quarter * 32 + threadIdx.x / Q_GROUPS;
+  const int64_t row = int64_t(blockIdx.y) * 128 + row_in_block;
   uint32_t scale_word = 0;
-  if (row < rows) {
+  if (row < rows && group < k_groups) {
+    const int live = int(min(int64_t(4), k_blocks - group * 4));  // scale blocks this thread owns
+    // Every load of the thread is issued before any value is used.
+    uint4 raw[4][LOADS];
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(x) +
+                                                      (row * k + group * 4 * BLOCK) * (F32_IN ? 4 : 2));
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < LOADS; ++i)
+        if (j < live) raw[j][i] = __ldg(src + j * LOADS + i);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
+      if (j >= live) break;
       const int64_t kb = group * 4 + j;
-      if (kb >= k_blocks) break;
       float v[BLOCK];
-      const int64_t at = row * k + kb * BLOCK;
-      if constexpr (F32_IN) {
-        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(x) + at);
 #pragma unroll
-        for (int i = 0; i < BLOCK / 4; ++i) {
-          const float4 q = __ldg(src + i);
-          v[4 * i] = q.x, v[4 * i + 1] = q.y, v[4 * i + 2] = q.z, v[4 * i + 3] = q.w;
-        }
-      } else {
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + at);
+      for (int i = 0; i < LOADS; ++i) {
+        const uint32_t w[4] = {raw[j][i].x, raw[j][i].y, raw[j][i].z, raw[j][i].w};
 #pragma unroll
-        for (int i = 0; i < BLOCK / 8; ++i) {
-          const uint4 q = __ldg(src + i);
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
+        for (int h = 0; h < 4; ++h) {
+          if constexpr (F32_IN) {
+            v[4 * i + h] = __uint_as_float(w[h]);
+          } else {
             v[8 * i + 2 * h] = __uint_as_float(w[h] << 16);
             v[8 * i + 2 * h + 1] = __uint_as_float(w[h] & 0xFFFF0000u);
           }
@@ -134,37 +188,47 @@ __global__ void __launch_bounds__(128) quantize_kernel(const void* __restrict__ 
       float amax = 0.f;
 #pragma unroll
       for (int i = 0; i < BLOCK; ++i) amax = fmaxf(amax, fabsf(v[i]));
-      float scale = fmaxf(__fdiv_rn(amax, TOP), 1e-30f);
+      const float scale = fmaxf(__fdiv_rn(amax, TOP), 1e-30f);
       uint32_t stored;
-      float stored_value;
+      float divisor, inverse = 0.f;
       if constexpr (FORMAT == Q_NVFP4) {
         stored = to_e4m3(scale);
-        stored_value = from_e4m3(stored);
+        divisor = fmaxf(from_e4m3(stored), 1e-30f);
       } else {
-        // 2^ceil(log2(scale)): the exponent, plus one when any mantissa bit is set
+        // 2^ceil(log2(scale)): the exponent, plus one when any mantissa bit is
+        // set (the 1e-30 floor keeps `scale` a normal float).  Dividing by a
+        // power of two is multiplying by its reciprocal, exactly.
         const uint32_t bits = __float_as_uint(scale);
-        int exponent = int(bits >> 23) - 127 + ((bits & 0x7FFFFFu) ? 1 : 0);
-        if ((bits >> 23) == 0) exponent = -126;  // float32 subnormals: not reachable after the 1e-30 floor
+        const int exponent = int(bits >> 23) - 127 + ((bits & 0x7FFFFFu) ? 1 : 0);
         stored = uint32_t(exponent + 127);
-        stored_value = __uint_as_float(stored << 23);
+        divisor = __uint_as_float(stored << 23);
+        inverse = (exponent <= 126) ? __uint_as_float(uint32_t(127 - exponent) << 23) : 0.f;
       }
-      const float divisor = fmaxf(stored_value, 1e-30f);
-      // A ue4m3 scale past the format's range is stored as NaN; dividing by it
-      // makes every value NaN, which the reference's nearest-code scan leaves
-      // at code 0.
-      const bool nan_scale = FORMAT == Q_NVFP4 && (stored & 0x7Fu) == 0x7Fu;
       scale_word |= stored << (8 * j);
       if (scales) scales[row * k_blocks + kb] = uint8_t(stored);
-      // quantise through bfloat16, as the reference does
+
+      // quotients, rounded through bfloat16 as the reference does
+      float q[BLOCK];
+      const bool by_inverse = FORMAT != Q_NVFP4 && inverse != 0.f;
+#pragma unroll
+      for (int i = 0; i < BLOCK; ++i)
+        q[i] = through_bf16(by_inverse ? v[i] * inverse : __fdiv_rn(v[i], divisor));
+
       if constexpr (FP4) {
+        // A ue4m3 scale past the format's range is stored as NaN: every quotient
+        // is then NaN, which the reference's nearest-code scan leaves at code 0.
+        const bool nan_scale = FORMAT == Q_NVFP4 && (stored & 0x7Fu) == 0x7Fu;
+        // Quotients far outside +-6 (the scale underflowed) need the literal scan.
+        const bool literal = !(through_bf16(__fdiv_rn(amax, divisor)) < 64.0f);
         uint32_t words[BLOCK / 8];
 #pragma unroll
         for (int i = 0; i < BLOCK / 8; ++i) {
           uint32_t w = 0;
+          if (literal) {
 #pragma unroll
-          for (int h = 0; h < 8; ++h) {
-            const float q = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(v[8 * i + h], divisor)));
-            w |= to_e2m1(q) << (4 * h);
+            for (int h = 0; h < 8; ++h) w |= to_e2m1(q[8 * i + h]) << (4 * h);
+          } else {
+            w = pack_e2m1x8(q + 8 * i);
           }
           words[i] = nan_scale ? 0u : w;
         }
@@ -177,26 +241,26 @@ __global__ void __launch_bounds__(128) quantize_kernel(const void* __restrict__ 
       } else {
         uint32_t words[BLOCK / 4];
 #pragma unroll
-        for (int i = 0; i < BLOCK / 4; ++i) {
-          uint32_t w = 0;
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const float q = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(v[4 * i + h], divisor)));
-            w |= to_e4m3(q) << (8 * h);
-          }
-          words[i] = w;
-        }
+        for (int i = 0; i < BLOCK / 4; ++i) words[i] = pack_e4m3x4(q + 4 * i);
         uint4* dst = reinterpret_cast<uint4*>(packed + row * k + kb * BLOCK);
         dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
         dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
       }
     }
   }
+  scale_words[group_in_cta][row_in_block] = scale_word;  // zero for rows and groups past the end
+  }
   if (blocked) {
-    // Rows past the end pad the last 128-row block with zero scales.
-    const int64_t atom = int64_t(blockIdx.y) * k_groups + group;
-    const uint32_t r = threadIdx.x;
-    *reinterpret_cast<uint32_t*>(blocked + atom * 512 + (r & 31) * 16 + (r >> 5) * 4) = scale_word;
+    // Whole atoms, 128 words each: word (r % 32) * 4 + r / 32 holds row r's four scales.
+    __syncthreads();
+    const int64_t first_group = int64_t(blockIdx.x) * Q_GROUPS;
+    for (int i = threadIdx.x; i < Q_GROUPS * 128; i += Q_THREADS) {
+      const int g = i >> 7, word = i & 127;
+      if (first_group + g >= k_groups) break;
+      const int r = (word & 3) * 32 + (word >> 2);
+      uint32_t* atom = reinterpret_cast<uint32_t*>(blocked + (int64_t(blockIdx.y) * k_groups + first_group + g) * 512);
+      atom[word] = scale_words[g][r];
+    }
   }
 }
 
@@ -239,14 +303,14 @@ OG_API int32_t og_b200_quantize(const char* format, const void* x, int32_t x_is_
   const int64_t k_groups = (k / block + 3) / 4;
   const int64_t row_blocks = (rows + 127) / 128;
   if (k_groups > 0x7FFFFFFF || row_blocks > 65535) return quantize_fail("the operand is too large for one launch");
-  const dim3 grid{unsigned(k_groups), unsigned(row_blocks), 1};
+  const dim3 grid{unsigned((k_groups + Q_GROUPS - 1) / Q_GROUPS), unsigned(row_blocks), 1};
   const cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint8_t* p = static_cast<uint8_t*>(packed);
   uint8_t* sc = static_cast<uint8_t*>(scales);
   uint8_t* sb = static_cast<uint8_t*>(scales_blocked);
 #define OG_QUANTIZE(F)                                                                      \
-  if (x_is_f32) quantize_kernel<F, true><<<grid, 128, 0, s>>>(x, rows, k, p, sc, sb);       \
-  else quantize_kernel<F, false><<<grid, 128, 0, s>>>(x, rows, k, p, sc, sb)
+  if (x_is_f32) quantize_kernel<F, true><<<grid, Q_THREADS, 0, s>>>(x, rows, k, p, sc, sb); \
+  else quantize_kernel<F, false><<<grid, Q_THREADS, 0, s>>>(x, rows, k, p, sc, sb)
   if (which == Q_NVFP4) { OG_QUANTIZE(Q_NVFP4); }
   else if (which == Q_MXFP8) { OG_QUANTIZE(Q_MXFP8); }
   else { OG_QUANTIZE(Q_MXFP4); }
