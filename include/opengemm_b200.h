@@ -137,6 +137,16 @@ OG_API int32_t og_b200_quantize(const char* format, const void* x, int32_t x_is_
                                 int32_t device, void* stream);
 OG_API const char* og_b200_quantize_error(void);
 
+/* Launches use programmatic dependent launch: the next kernel of a stream may start
+ * while this one drains.  By default every global-memory access of a kernel first
+ * waits for the previous kernel to complete, so chained GEMMs (C of one feeding the
+ * next) are safe.  With `yes` != 0 the caller vouches, process-wide, that no earlier
+ * kernel in the stream writes the A / B / scale operands of a launch (weights and
+ * inputs already resident, as in a benchmark loop): operand loads then start without
+ * waiting, and only the stores wait - which is the only mode the reference has
+ * (opengemm/src/mm/kernel.cuh:209,479-483).  Default 0. */
+OG_API void og_b200_set_independent_inputs(int32_t yes);
+
 /* Limit of every device-side wait in milliseconds (default 2000). */
 OG_API void og_b200_set_wait_limit_ms(int32_t ms);
 

@@ -133,6 +133,8 @@ class Library:
             self._checked.argtypes = [POINTER(OgGemm)] + [c_void_p] * 5 + [c_int32, c_void_p, c_void_p]
             self._set_limit = lib.og_b200_set_wait_limit_ms
             self._set_limit.restype, self._set_limit.argtypes = None, [c_int32]
+            self._independent = lib.og_b200_set_independent_inputs
+            self._independent.restype, self._independent.argtypes = None, [c_int32]
             self._quantize = lib.og_b200_quantize
             self._quantize.restype = c_int32
             self._quantize.argtypes = [c_char_p, c_void_p, c_int32, ctypes.c_int64, ctypes.c_int64, c_void_p, c_void_p,
@@ -228,6 +230,10 @@ class Library:
         )
         if status != OG_OK:
             raise RuntimeError(self._quantize_error().decode())
+
+    def set_independent_inputs(self, yes):
+        """Vouch (or stop vouching) that no earlier kernel of the stream writes a launch's operands."""
+        self._independent(int(bool(yes)))
 
     def set_wait_limit_ms(self, ms):
         self._set_limit(int(ms))

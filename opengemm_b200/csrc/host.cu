@@ -45,6 +45,7 @@ namespace {
 
 thread_local char error_text[320];
 std::atomic<long long> wait_limit_ns{2000ll * 1000 * 1000};
+std::atomic<int> independent_inputs{0};
 
 int fail(int code, const char* format, ...) {
   va_list args;
@@ -361,7 +362,7 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
   params.sf_yblocks = p.sf_yblocks;
   params.k_groups = p.k_groups;
   static const bool pdl_enabled = [] { const char* e = getenv("OPENGEMM_PDL"); return !(e && e[0] == '0'); }();
-  params.pdl = pdl_enabled ? 1 : 0;
+  params.pdl = pdl_enabled ? (independent_inputs.load(std::memory_order_relaxed) ? 2 : 1) : 0;
 
   const int sm_count = sm_count_of(device);
   int grid = grid_for(p, sm_count);
@@ -513,6 +514,8 @@ OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, in
   if (wrote < 0 || wrote >= cap) return fail(OG_ERR_BIND, "the buffer of %d bytes is too small for the description", cap);
   return OG_OK;
 }
+
+OG_API void og_b200_set_independent_inputs(int32_t yes) { independent_inputs.store(yes ? 1 : 0); }
 
 OG_API void og_b200_set_wait_limit_ms(int32_t ms) {
   wait_limit_ns.store((long long)std::max(1, (int)ms) * 1000000ll);

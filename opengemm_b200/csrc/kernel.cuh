@@ -61,7 +61,8 @@ struct alignas(64) GemmParams {
   int sf_atoms;           // 512-byte scale atoms per stage per 128-row block
   int sf_yblocks;         // 128-row blocks of N-side scales per tile (1 or 2)
   int k_groups;           // atoms along K of the global scale buffers
-  int pdl;                // wait for the previous grid before touching memory
+  int pdl;                // 1: every global access waits for the previous grid; 2: only the stores do
+                          // (the caller vouches that no earlier kernel of the stream writes the operands)
   // Stream-K: the (tile, K-block) units are dealt out in equal contiguous
   // ranges, so a range may begin or end inside a tile.  See WorkIter.
   int use_clc;            // tiles come from cluster launch control instead of a fixed stride
@@ -306,7 +307,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     // One thread; the loop body is kept to a handful of instructions per
     // stage (ring position and phase advance by increment, never by division).
     if (elect_one()) {
-      if (p.pdl) pdl_wait_prior_grids();
+      if (p.pdl == 1) pdl_wait_prior_grids();
+      // Plan values used every stage live in registers: the inline PTX below
+      // clobbers memory, which would otherwise force a constant-bank reload
+      // of each p.field per iteration.
+      const int stages = p.stages, block_k = p.block_k;
+      const uint32_t stage_bytes = p.stage_bytes, x_bytes = p.x_bytes, tx_bytes = p.tx_bytes;
+      const bool two_sfy = p.sf_yblocks == 2;
       const int y_rows = p.tile_n / CTA_GROUP;
       const uint32_t sfx_off = p.x_bytes + p.y_bytes;
       const uint32_t sf_block_bytes = p.sf_atoms * 512;
@@ -326,7 +333,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         const int row_y = t.ni * p.tile_n + int(rank) * y_rows;
         int sfx_row = 2 * (row_x >> 7) * p.k_groups + w.kb0 * sf_step;
         int sfy_row = 2 * ((t.ni * p.tile_n) >> 7) * p.k_groups + w.kb0 * sf_step;
-        int kx = w.kb0 * p.block_k;
+        int kx = w.kb0 * block_k;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, ctx, SITE_PRODUCER_EMPTY)) {
             ok = false;
@@ -334,23 +341,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           }
           const uint32_t full_local = bar_full + 8 * stage;
           const uint32_t full = (CTA_GROUP == 2) ? map_to_cta(full_local, 0) : full_local;
-          if (rank == 0) mbar_expect_tx(full_local, p.tx_bytes);
-          const uint32_t sx = ring + stage * p.stage_bytes;
+          if (rank == 0) mbar_expect_tx(full_local, tx_bytes);
+          const uint32_t sx = ring + stage * stage_bytes;
           tma_load_2d<CTA_GROUP>(sx, &params.map_x, kx, row_x, full);
-          tma_load_2d<CTA_GROUP>(sx + p.x_bytes, &params.map_y, kx, row_y, full);
+          tma_load_2d<CTA_GROUP>(sx + x_bytes, &params.map_y, kx, row_y, full);
           if constexpr (SCALED) {
             const uint32_t ssfx = sx + sfx_off;
             tma_load_2d<CTA_GROUP>(ssfx, &params.map_sfx, 0, sfx_row, full);
             tma_load_2d<CTA_GROUP>(ssfx + sf_block_bytes, &params.map_sfy, 0, sfy_row, full);
-            if (p.sf_yblocks == 2)
+            if (two_sfy)
               tma_load_2d<CTA_GROUP>(ssfx + 2 * sf_block_bytes, &params.map_sfy, 0,
                                      sfy_row + sf_block_step, full);
             sfx_row += sf_step;
             sfy_row += sf_step;
           }
-          kx += p.block_k;
+          kx += block_k;
           ++issued;
-          if (++stage == p.stages) stage = 0, phase ^= 1;
+          if (++stage == stages) stage = 0, phase ^= 1;
         }
       }
       if (!ok && rank == 0) {
@@ -387,6 +394,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       const uint64_t dsf0 = scale_desc(ring + p.x_bytes + p.y_bytes);
       const bool two_yblocks = p.sf_yblocks == 2;
       const int yb = p.sf_yblocks;
+      const int stages = p.stages, block_k = p.block_k, mma_k = p.mma_k, k_total = p.k;
+      const uint32_t idesc = p.idesc, acc_stride = p.acc_stride, sf_base = tmem_base + p.sf_col, sf_cols = p.sf_cols;
+      const bool two_acc = p.acc_slots == 2, two_sf = p.sf_slots == 2;
       int stage = 0;
       uint32_t phase = 0;
       uint64_t stage_off = 0;  // stage * (stage_bytes >> 4)
@@ -397,27 +407,29 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       if (p.use_clc) work.enable_clc(clc_state(false, true), CTA_GROUP);
       Work w;
       for (; ok && work.next(w); ++tile_idx) {
-        const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
-        const uint32_t use = (p.acc_slots == 2) ? (tile_idx >> 1) : tile_idx;
+        const int slot = two_acc ? (tile_idx & 1) : 0;
+        const uint32_t use = two_acc ? (tile_idx >> 1) : tile_idx;
         if (!mbar_wait(bar_acc_empty + 8 * slot, (use & 1) ^ 1, ctx, SITE_MMA_ACC_EMPTY)) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + slot * p.acc_stride;
+        const uint32_t d_tmem = tmem_base + slot * acc_stride;
         uint32_t sfy_shift = 0;
         if constexpr (SCALED) {
           const TileCoord t = tile_coord(p, w.tile);
           sfy_shift = ((t.ni * p.tile_n) & 127) >> 5;  // tile origin inside its 128-row scale block
         }
         uint32_t accumulate = 0;
-        int k_left = p.k - w.kb0 * p.block_k;
+        int k_left = k_total - w.kb0 * block_k;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, ctx, SITE_MMA_FULL)) {
             ok = false;
             break;
           }
-          tc_fence_after_sync();
+          // No tcgen05 fence here: the stage was written by TMA (async proxy)
+          // and is read by tcgen05.mma / cp through the same proxy, ordered by
+          // the barrier's completion.
           uint32_t sfx_tmem = 0, sfy_tmem = 0;
           if constexpr (SCALED) {
-            sfx_tmem = tmem_base + p.sf_col + sf_slot * p.sf_cols;
+            sfx_tmem = sf_base + sf_slot * sf_cols;
             sfy_tmem = sfx_tmem + 4 * SF_ATOMS;
             const uint64_t dsf = dsf0 + stage_off;
 #pragma unroll
@@ -427,7 +439,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
               if (two_yblocks)
                 scale_copy<CTA_GROUP>(sfy_tmem + 4 * w * yb + 4, dsf + 32 * (2 * SF_ATOMS + w));
             }
-            sf_slot = (p.sf_slots == 2) ? (sf_slot ^ 1) : 0;
+            sf_slot = two_sf ? (sf_slot ^ 1) : 0;
           }
           const uint64_t dx = dx0 + stage_off;
           const uint64_t dy = dy0 + stage_off;
@@ -436,24 +448,24 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
             // Past the end of K a stage holds TMA's zero fill; an MMA that
             // would read only that is skipped.  Each MMA covers 32 bytes of
             // every row, two 16-byte units of the descriptor's start field.
-            if (ki == 0 || ki * p.mma_k < k_left) {
+            if (ki == 0 || ki * mma_k < k_left) {
               if constexpr (SCALED) {
                 constexpr int NVF4 = KIND == KIND_NVF4, MXF4 = KIND == KIND_MXF4;
                 const int atom = NVF4 ? ki : MXF4 ? (ki >> 1) : 0;
                 const uint32_t id = NVF4 ? 0u : MXF4 ? uint32_t((ki & 1) * 2) : uint32_t(ki);
                 mma_scaled<KIND, CTA_GROUP>(d_tmem, dx + 2 * ki, dy + 2 * ki,
-                                            p.idesc | (id << 29) | (id << 4), sfx_tmem + 4 * atom,
+                                            idesc | (id << 29) | (id << 4), sfx_tmem + 4 * atom,
                                             sfy_tmem + 4 * atom * yb + sfy_shift, accumulate);
               } else {
-                mma_dense<KIND, CTA_GROUP>(d_tmem, dx + 2 * ki, dy + 2 * ki, p.idesc, accumulate);
+                mma_dense<KIND, CTA_GROUP>(d_tmem, dx + 2 * ki, dy + 2 * ki, idesc, accumulate);
               }
               accumulate = 1;
             }
           }
           mma_commit<CTA_GROUP>(bar_empty + 8 * stage);
-          k_left -= p.block_k;
+          k_left -= block_k;
           stage_off += desc_stage;
-          if (++stage == p.stages) stage = 0, phase ^= 1, stage_off = 0;
+          if (++stage == stages) stage = 0, phase ^= 1, stage_off = 0;
         }
         if (ok) mma_commit<CTA_GROUP>(bar_acc_full + 8 * slot);
       }
@@ -468,6 +480,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     constexpr int CHUNK = (OUT_BYTES == 2) ? 64 : 32;  // columns per 128-byte staging row
     int buf_use = 0;
     bool touched_memory = false;
+    const int tile_n = p.tile_n, rows_m = p.rows_m, rows_n = p.rows_n, ldd = p.ldd;
+    const bool epi_tma = p.epi_tma != 0, transpose_out = p.transpose_out != 0, vec_ok = p.vec_ok != 0;
+    uint8_t* const out = static_cast<uint8_t*>(p.d);
     int tile_idx = 0;
     // Stream-K bookkeeping: this warp's region of the partial-sum workspace
     // and its neighbour's (the same warp of the next cluster).
@@ -490,11 +505,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
 
       const int row0 = t.mi * TILE_M + int(rank) * 128 + quarter * 32;  // first row of this warp
       const int row = row0 + lane;
-      const int col0 = t.ni * p.tile_n;
+      const int col0 = t.ni * tile_n;
       const uint32_t acc_tmem = tmem_base + lane_base + slot * p.acc_stride;
 
-      for (int c = 0; c < p.tile_n && col0 + c < p.rows_n; c += CHUNK) {
-        const int width = min(CHUNK, p.tile_n - c);
+      for (int c = 0; c < tile_n && col0 + c < rows_n; c += CHUNK) {
+        const int width = min(CHUNK, tile_n - c);
         uint32_t v[CHUNK];
         if (width >= 32) tmem_ld_32(acc_tmem + c, v);
         else tmem_ld_16(acc_tmem + c, v);
@@ -552,7 +567,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           continue;
         }
 
-        if (p.epi_tma && width == CHUNK && row0 < p.rows_m) {
+        if (epi_tma && width == CHUNK && row0 < rows_m) {
           // Stage 32 rows x 128 bytes with the 128-byte swizzle (16-byte unit
           // index XOR row%8), then one lane stores the box with TMA, which
           // clips it at the edges of D.
@@ -582,19 +597,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
             tma_store_2d(&params.map_d, buf, col0 + c, row0);
             tma_store_commit();
           }
-        } else if (!p.transpose_out) {
-          if (row < p.rows_m) {
+        } else if (!transpose_out) {
+          if (row < rows_m) {
             const int gc = col0 + c;
-            if (p.vec_ok && gc + width <= p.rows_n) {
+            if (vec_ok && gc + width <= rows_n) {
               if constexpr (OUT_BYTES == 4) {
-                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.d) +
-                                                      size_t(row) * p.ldd + gc);
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) +
+                                                      size_t(row) * ldd + gc);
 #pragma unroll
                 for (int u = 0; u < CHUNK / 4; ++u)
                   if (4 * u < width) dst[u] = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
               } else {
-                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.d) +
-                                                      size_t(row) * p.ldd + gc);
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) +
+                                                      size_t(row) * ldd + gc);
 #pragma unroll
                 for (int u = 0; u < CHUNK / 8; ++u)
                   if (8 * u < width)
@@ -607,12 +622,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
             } else {
 #pragma unroll
               for (int j = 0; j < CHUNK; ++j) {
-                if (j < width && gc + j < p.rows_n) {
-                  const size_t at = size_t(row) * p.ldd + gc + j;
+                if (j < width && gc + j < rows_n) {
+                  const size_t at = size_t(row) * ldd + gc + j;
                   if constexpr (OUT_BYTES == 4)
-                    static_cast<uint32_t*>(p.d)[at] = v[j];
+                    reinterpret_cast<uint32_t*>(out)[at] = v[j];
                   else
-                    static_cast<uint16_t*>(p.d)[at] =
+                    reinterpret_cast<uint16_t*>(out)[at] =
                         uint16_t(pack_bf16x2(__uint_as_float(v[j]), 0.f) & 0xFFFFu);
                 }
               }
@@ -621,16 +636,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         } else {
           // Transposed output: this thread's MMA row is an output column, so
           // the lanes of a warp write consecutive elements of one output row.
-          if (row < p.rows_m) {
+          if (row < rows_m) {
 #pragma unroll
             for (int j = 0; j < CHUNK; ++j) {
               const int orow = col0 + c + j;
-              if (j < width && orow < p.rows_n) {
-                const size_t at = size_t(orow) * p.ldd + row;
+              if (j < width && orow < rows_n) {
+                const size_t at = size_t(orow) * ldd + row;
                 if constexpr (OUT_BYTES == 4)
-                  static_cast<uint32_t*>(p.d)[at] = v[j];
+                  reinterpret_cast<uint32_t*>(out)[at] = v[j];
                 else
-                  static_cast<uint16_t*>(p.d)[at] =
+                  reinterpret_cast<uint16_t*>(out)[at] =
                       uint16_t(pack_bf16x2(__uint_as_float(v[j]), 0.f) & 0xFFFFu);
               }
             }

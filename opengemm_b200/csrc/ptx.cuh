@@ -106,14 +106,18 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
                : "memory");
 }
 
+// One attempt: the hardware parks the thread until the phase completes or the
+// hint (nanoseconds) runs out, so a waiting role does not burn issue slots and
+// power spinning - on a power-capped part that is tensor-core clock.
+constexpr uint32_t WAIT_PARK_NS = 1000000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(WAIT_PARK_NS)
       : "memory");
   return done != 0;
 }
