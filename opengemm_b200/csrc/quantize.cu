@@ -11,14 +11,12 @@
 //   value  = bf16(x / float(stored))           then the nearest element value,
 //            a tie going to the even code
 //
-// One thread owns four consecutive scale blocks of one row (64 values for
-// nvfp4, 128 for the mx formats): it reads them with 16-byte loads, writes
-// 32-128 contiguous bytes of packed output and one 32-bit word of four scales.
-// Neighbouring lanes own neighbouring groups of the same row, so a warp reads
-// and writes contiguous kilobytes; a CTA covers 128 rows x 8 groups and writes
-// its eight 512-byte atoms of the blocked scale layout whole.  HBM-bound: 2
-// (bf16) or 4 (f32) bytes read and 0.5-1 byte plus 1/16-1/32 byte written per
-// value.
+// One thread quantises one scale block at a time (16 or 32 values) with
+// 16-byte loads and stores; the lanes of a warp take consecutive blocks of a
+// row, so a warp reads and writes contiguous kilobytes; a CTA covers 128 rows
+// x 32 blocks and writes its eight 512-byte atoms of the blocked scale layout
+// whole.  HBM-bound: 2 (bf16) or 4 (f32) bytes read and 0.5-1 byte plus
+// 1/16-1/32 byte written per value.
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -131,14 +129,30 @@ __device__ __forceinline__ float through_bf16(float x) {
 }
 
 constexpr int Q_THREADS = 256;
-constexpr int Q_GROUPS = 8;  // K groups (of four scale blocks) per CTA
+constexpr int Q_GROUPS = 8;                 // K groups (of four scale blocks) per CTA
+constexpr int Q_BLOCKS = Q_GROUPS * 4;      // scale blocks along K per CTA
 
-// A CTA covers 128 rows x 8 K groups.  Eight consecutive lanes read one row's
-// eight groups, 1-2 KiB of contiguous input; the CTA walks the four 32-row
-// quarters of its row block, collects the scale words in shared memory and
-// then writes its eight 512-byte scale atoms whole.
+// x / s, correctly rounded, for a divisor that is a ue4m3 value (at most four
+// significant bits).  q0 = x * (1/s) is refined once with the exact residual;
+// the true quotient a / b (a < 2^24, b <= 15 after scaling) is either exactly
+// representable or at least 2^-30 (relative) away from every float32
+// rounding boundary, far more than the refined value's error, so the result
+// equals IEEE division.  Tiny numerators, whose quotient could be subnormal,
+// take the library division.
+__device__ __forceinline__ float divide_exact(float x, float s, float inverse) {
+  if (fabsf(x) < 1e-30f) return __fdiv_rn(x, s);
+  const float q0 = x * inverse;
+  const float residual = __fmaf_rn(-q0, s, x);
+  return __fmaf_rn(residual, inverse, q0);
+}
+
+// A CTA covers 128 rows x 32 scale blocks.  One thread quantises one scale
+// block at a time (16 or 32 values, 32-128 bytes of input); the 32 lanes of a
+// warp take the 32 consecutive blocks of one row, 1-4 KiB of contiguous
+// input, and the CTA's eight warps walk the 128 rows sixteen at a time.  Scale
+// bytes collect in shared memory and leave as whole 512-byte atoms.
 template <int FORMAT, bool F32_IN>
-__global__ void __launch_bounds__(Q_THREADS, F32_IN ? 1 : 2) quantize_kernel(const void* __restrict__ x, int64_t rows, int64_t k,
+__global__ void __launch_bounds__(Q_THREADS) quantize_kernel(const void* __restrict__ x, int64_t rows, int64_t k,
                                                              uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
                                                              uint8_t* __restrict__ blocked) {
   constexpr int BLOCK = FORMAT == Q_NVFP4 ? 16 : 32;  // values per scale
@@ -148,33 +162,26 @@ __global__ void __launch_bounds__(Q_THREADS, F32_IN ? 1 : 2) quantize_kernel(con
   constexpr int LOADS = BLOCK / VEC;                  // loads per scale block
   const int64_t k_blocks = k / BLOCK;
   const int64_t k_groups = (k_blocks + 3) / 4;
-  __shared__ uint32_t scale_words[Q_GROUPS][128];
-  const int group_in_cta = threadIdx.x % Q_GROUPS;
-  const int64_t group = int64_t(blockIdx.x) * Q_GROUPS + group_in_cta;  // four scale blocks along K
-#pragma unroll 1
-  for (int quarter = 0; quarter < 4; ++quarter) {
-  const int row_in_block = quarter * 32 + threadIdx.x / Q_GROUPS;
-  const int64_t row = int64_t(blockIdx.y) * 128 + row_in_block;
-  uint32_t scale_word = 0;
-  if (row < rows && group < k_groups) {
-    const int live = int(min(int64_t(4), k_blocks - group * 4));  // scale blocks this thread owns
-    // Every load of the thread is issued before any value is used.
-    uint4 raw[4][LOADS];
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(x) +
-                                                      (row * k + group * 4 * BLOCK) * (F32_IN ? 4 : 2));
+  __shared__ uint8_t scale_bytes[128][Q_BLOCKS + 4];  // [row][block]; the pad spreads banks
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t kb = int64_t(blockIdx.x) * Q_BLOCKS + lane;  // this lane's scale block along K
+  const bool live_block = kb < k_blocks;
+
+#pragma unroll 2
+  for (int step = 0; step < 16; ++step) {
+    const int row_in_block = step * 8 + warp;
+    const int64_t row = int64_t(blockIdx.y) * 128 + row_in_block;
+    uint32_t stored = 0;
+    if (row < rows && live_block) {
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(x) +
+                                                        (row * k + kb * BLOCK) * (F32_IN ? 4 : 2));
+      uint4 raw[LOADS];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int i = 0; i < LOADS; ++i)
-        if (j < live) raw[j][i] = __ldg(src + j * LOADS + i);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (j >= live) break;
-      const int64_t kb = group * 4 + j;
+      for (int i = 0; i < LOADS; ++i) raw[i] = __ldg(src + i);
       float v[BLOCK];
 #pragma unroll
       for (int i = 0; i < LOADS; ++i) {
-        const uint32_t w[4] = {raw[j][i].x, raw[j][i].y, raw[j][i].z, raw[j][i].w};
+        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
           if constexpr (F32_IN) {
@@ -188,12 +195,17 @@ __global__ void __launch_bounds__(Q_THREADS, F32_IN ? 1 : 2) quantize_kernel(con
       float amax = 0.f;
 #pragma unroll
       for (int i = 0; i < BLOCK; ++i) amax = fmaxf(amax, fabsf(v[i]));
-      const float scale = fmaxf(__fdiv_rn(amax, TOP), 1e-30f);
-      uint32_t stored;
-      float divisor, inverse = 0.f;
+      // amax / 6 and amax / 448 by the same exact reciprocal refinement (3 and 7
+      // are the divisors' odd parts); tiny or huge amax takes the library division.
+      constexpr float TOP_INVERSE = 1.0f / TOP;
+      const float scale = fmaxf((amax > 1e-20f && amax < 1e30f) ? divide_exact(amax, TOP, TOP_INVERSE) : __fdiv_rn(amax, TOP), 1e-30f);
+      float divisor, inverse;
+      bool exact_inverse;  // `inverse` is exactly 1 / divisor (a power of two)
       if constexpr (FORMAT == Q_NVFP4) {
         stored = to_e4m3(scale);
         divisor = fmaxf(from_e4m3(stored), 1e-30f);
+        inverse = __frcp_rn(divisor);
+        exact_inverse = false;
       } else {
         // 2^ceil(log2(scale)): the exponent, plus one when any mantissa bit is
         // set (the 1e-30 floor keeps `scale` a normal float).  Dividing by a
@@ -202,24 +214,38 @@ __global__ void __launch_bounds__(Q_THREADS, F32_IN ? 1 : 2) quantize_kernel(con
         const int exponent = int(bits >> 23) - 127 + ((bits & 0x7FFFFFu) ? 1 : 0);
         stored = uint32_t(exponent + 127);
         divisor = __uint_as_float(stored << 23);
-        inverse = (exponent <= 126) ? __uint_as_float(uint32_t(127 - exponent) << 23) : 0.f;
+        exact_inverse = exponent <= 126;
+        inverse = exact_inverse ? __uint_as_float(uint32_t(127 - exponent) << 23) : 0.f;
       }
-      scale_word |= stored << (8 * j);
       if (scales) scales[row * k_blocks + kb] = uint8_t(stored);
 
       // quotients, rounded through bfloat16 as the reference does
+      // A ue4m3 scale that underflowed to zero (divisor 1e-30) or overflowed to NaN
+      // is rare: those blocks take the library division.
+      const bool plain = FORMAT == Q_NVFP4 && ((stored & 0x7Fu) == 0x7Fu || (stored & 0x7Fu) == 0u);
       float q[BLOCK];
-      const bool by_inverse = FORMAT != Q_NVFP4 && inverse != 0.f;
 #pragma unroll
-      for (int i = 0; i < BLOCK; ++i)
-        q[i] = through_bf16(by_inverse ? v[i] * inverse : __fdiv_rn(v[i], divisor));
+      for (int i = 0; i < BLOCK; i += 2) {
+        float pair[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (exact_inverse) pair[h] = v[i + h] * inverse;
+          else if (FORMAT != Q_NVFP4 || plain) pair[h] = __fdiv_rn(v[i + h], divisor);
+          else pair[h] = divide_exact(v[i + h], divisor, inverse);
+        }
+        uint32_t both;  // two quotients rounded to bfloat16 in one instruction
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(both) : "f"(pair[1]), "f"(pair[0]));
+        q[i] = __uint_as_float(both << 16);
+        q[i + 1] = __uint_as_float(both & 0xFFFF0000u);
+      }
 
       if constexpr (FP4) {
         // A ue4m3 scale past the format's range is stored as NaN: every quotient
         // is then NaN, which the reference's nearest-code scan leaves at code 0.
         const bool nan_scale = FORMAT == Q_NVFP4 && (stored & 0x7Fu) == 0x7Fu;
         // Quotients far outside +-6 (the scale underflowed) need the literal scan.
-        const bool literal = !(through_bf16(__fdiv_rn(amax, divisor)) < 64.0f);
+        // (amax >= 32 x divisor is a cheap superset of "some quotient reaches 64".)
+        const bool literal = !(amax < 32.0f * divisor);
         uint32_t words[BLOCK / 8];
 #pragma unroll
         for (int i = 0; i < BLOCK / 8; ++i) {
@@ -247,19 +273,20 @@ __global__ void __launch_bounds__(Q_THREADS, F32_IN ? 1 : 2) quantize_kernel(con
         dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
       }
     }
-  }
-  scale_words[group_in_cta][row_in_block] = scale_word;  // zero for rows and groups past the end
+    scale_bytes[row_in_block][lane] = uint8_t(stored);  // zero for rows and blocks past the end
   }
   if (blocked) {
-    // Whole atoms, 128 words each: word (r % 32) * 4 + r / 32 holds row r's four scales.
+    // Whole atoms, 128 words each: word w holds the four scales of row
+    // (w % 4) * 32 + w / 4 for the atom's four scale blocks.
     __syncthreads();
     const int64_t first_group = int64_t(blockIdx.x) * Q_GROUPS;
     for (int i = threadIdx.x; i < Q_GROUPS * 128; i += Q_THREADS) {
       const int g = i >> 7, word = i & 127;
       if (first_group + g >= k_groups) break;
       const int r = (word & 3) * 32 + (word >> 2);
+      const uint8_t* four = &scale_bytes[r][4 * g];
       uint32_t* atom = reinterpret_cast<uint32_t*>(blocked + (int64_t(blockIdx.y) * k_groups + first_group + g) * 512);
-      atom[word] = scale_words[g][r];
+      atom[word] = uint32_t(four[0]) | (uint32_t(four[1]) << 8) | (uint32_t(four[2]) << 16) | (uint32_t(four[3]) << 24);
     }
   }
 }
