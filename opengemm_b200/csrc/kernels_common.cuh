@@ -17,11 +17,13 @@ cudaError_t launch_one(const GemmParams& params, int grid, int smem_bytes, cudaS
   config.stream = stream;
   cudaLaunchAttribute attrs[2];
   int count = 0;
-  attrs[count].id = cudaLaunchAttributeClusterDimension;
-  attrs[count].val.clusterDim.x = CTA_GROUP;
-  attrs[count].val.clusterDim.y = 1;
-  attrs[count].val.clusterDim.z = 1;
-  ++count;
+  if (CTA_GROUP > 1) {  // a single CTA needs no cluster launch
+    attrs[count].id = cudaLaunchAttributeClusterDimension;
+    attrs[count].val.clusterDim.x = CTA_GROUP;
+    attrs[count].val.clusterDim.y = 1;
+    attrs[count].val.clusterDim.z = 1;
+    ++count;
+  }
   if (pdl) {
     attrs[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[count].val.programmaticStreamSerializationAllowed = 1;
