@@ -17,7 +17,7 @@ import os
 import re
 from pathlib import Path
 
-from .dtypes import DTYPES
+from .dtypes import DTYPES, sf_block
 from .log import log
 
 PACKAGE = Path(__file__).resolve().parent
@@ -90,41 +90,94 @@ def _round_up(x, to):
     return -(-x // to) * to
 
 
+# Constants of the tile-time model below, fitted to measurements on B200.  A K
+# block (128 bytes of K per row) keeps the tensor pipe busy for 2 x tile_n SM
+# clocks; L2 feeds an SM's ring about 80 bytes per clock when every SM pulls at
+# once; the output leaves at the SM's share of HBM write bandwidth.  A long
+# tensor-bound kernel runs into the board's power limit, which holds the SM
+# clock near 1.35 GHz however the tiles are spread over the SMs, while a
+# critical path (the waves) runs at up to 1.9 GHz: a partly idle last wave
+# costs less than its share of tiles suggests.
+LOAD_BYTES_PER_CLOCK = 80.0
+STORE_BYTES_PER_CLOCK = 27.0
+DRAIN_CLOCKS = 600.0    # single-accumulator tiles: the MMA warp waits while tensor memory is read out
+TILE_CLOCKS = 400.0     # hand-offs per tile that nothing overlaps
+TRAFFIC_ENERGY = 0.25   # energy of moving a clock's worth of operand bytes, in tensor-pipe clocks
+BOOST_GHZ, CAPPED_GHZ = 1.9, 1.35
+HBM_BYTES_PER_US = 6.5e6
+HBM_SATURATING_CTAS = 96.0
+
+
+def _smem_bytes_per_value(name):
+    d = DTYPES[name]
+    if d.impl == "smm":
+        return 0.5 if d.bits == 4 else 1.0
+    return max(1.0, d.bits / 8)  # dense sub-byte values are unpacked to bytes by the tensor map
+
+
+def modelled_us(name, m, n, k, use_2cta, output_n, swap_ab):
+    """Estimated microseconds for one GEMM with the given tiling: the slower
+    of the critical path (waves x tile time at the boost clock, the K loop
+    bound by the tensor pipe or by L2 -> shared-memory traffic) and the
+    power-limited time of all tiles' work spread over the SMs."""
+    d = DTYPES[name]
+    scaled = d.impl == "smm"
+    rows_m, rows_n = (n, m) if swap_ab else (m, n)
+    cg = 2 if use_2cta else 1
+    block_k = 128 / _smem_bytes_per_value(name)
+    k_blocks = -(-k // int(block_k))
+    scale_bytes = 0.0
+    if scaled:
+        atoms = block_k / (4 * sf_block(d))
+        scale_bytes = atoms * 512 * (1 + (2 if output_n > 128 else 1))
+    slots = SM_COUNT // cg
+    tiles = -(-rows_m // (128 * cg)) * -(-rows_n // output_n)
+    waves = -(-tiles // slots)
+    compute = 2.0 * output_n
+    load = ((128 + output_n / cg) * 128 + scale_bytes) / LOAD_BYTES_PER_CLOCK
+    store = 128 * output_n * d.out.itemsize / STORE_BYTES_PER_CLOCK
+    extra = TILE_CLOCKS + (DRAIN_CLOCKS if scaled and output_n > 192 else 0.0)
+    tile = max(k_blocks * max(compute, load), store) + extra
+    energy = max(k_blocks * (compute + TRAFFIC_ENERGY * load), store) + extra
+    path_us = waves * tile / (BOOST_GHZ * 1e3)
+    power_us = tiles / slots * energy / (CAPPED_GHZ * 1e3)
+    # Operands and output cross HBM at least once; few CTAs cannot keep enough
+    # loads in flight to saturate it.
+    hbm_bytes = (m * k + n * k) * d.bits / 8 + m * n * d.out.itemsize
+    streams = min(1.0, min(tiles, slots) * cg / HBM_SATURATING_CTAS)
+    hbm_us = hbm_bytes / (HBM_BYTES_PER_US * streams)
+    return max(path_us, power_us, hbm_us) + store / (BOOST_GHZ * 1e3)
+
+
 def heuristic_config(name, m, n, k):
     """A configuration chosen by rule, for shapes nothing is stored for.
 
-    Small M rides the MMA's N side (swap_ab) so the 128-row side streams B;
-    pairs of CTAs take 256-row tiles once there are enough of them to fill the
-    GPU; the tile width is the widest the format allows, narrowed when that
-    wastes less of the last wave of 148 SMs.
+    Small M rides the MMA's N side (swap_ab) so the 128-row side streams B.
+    Pair size and tile width minimise `modelled_us`; estimates within 2 %
+    go to the pair and the wider tile (less operand traffic).
     """
     d = DTYPES[name]
     scaled = d.impl == "smm"
     swap = m <= 64 and n >= 2 * m
     rows_m, rows_n = (n, m) if swap else (m, n)
-    step = 64 if scaled else 16
-    widest = 256 if not scaled else 192
-    if rows_n <= widest:
-        output_n = max(16, _round_up(rows_n, 16))
-        if scaled and not (output_n < 64):
-            output_n = _round_up(output_n, 64)
-    else:
-        best = None
-        for cand in range(widest, 63, -step):
-            for two in (1, 0):
-                tile_m = 256 if two else 128
-                tiles = -(-rows_m // tile_m) * -(-rows_n // cand)
-                slots = SM_COUNT // (2 if two else 1)
-                waves = -(-tiles // slots)
-                # time ~ waves x tile work; prefer pairs (less operand traffic) on ties
-                cost = waves * tile_m * cand / (2 if two else 1) * (1.0 if two else 1.04)
-                if best is None or cost < best[0] - 1e-9:
-                    best = (cost, cand, two)
-        output_n = best[1]
-    tiles_pair = -(-rows_m // 256) * -(-rows_n // output_n)
-    use_2cta = int(rows_m >= 256 and output_n >= 32 and tiles_pair >= SM_COUNT // 4)
-    if rows_n > widest:
-        use_2cta = int(best[2] and rows_m >= 256)
+    # Widths that fill whole 128-byte lines of the staged rows.
+    step = 64 if (scaled or d.out.itemsize == 2) else 32
+    cap = _round_up(rows_n, 16)
+    if scaled and cap >= 64:
+        cap = _round_up(cap, 64)
+    widths = sorted({w for w in range(step, 257, step) if w <= cap} | ({cap} if cap < step or cap <= 256 and not scaled else set()))
+    widths = [w for w in widths if w <= 256] or [min(cap, 256)]
+    best = None
+    for two in (True, False):
+        if two and rows_m <= 128:
+            continue
+        for width in reversed(widths):
+            if two and width < 32:
+                continue
+            cost = modelled_us(name, m, n, k, two, width, swap)
+            if best is None or cost < best[0] * 0.98:
+                best = (cost, two, width)
+    _, use_2cta, output_n = best
     config = {
         "use_2cta": bool(use_2cta),
         "output_n": int(output_n),

@@ -7,8 +7,9 @@
 //   warp 1      owns tensor memory; one elected thread of the pair's leader
 //               copies scale atoms into tensor memory and issues tcgen05.mma
 //   warps 2-5   epilogue: tcgen05.ld the accumulator, convert, and store
-//               either straight to global memory or through swizzled staging
-//               buffers and per-warp TMA stores
+//               either each thread its own row, or through a swizzled
+//               staging buffer per warp from which every store instruction
+//               writes four rows x 128 contiguous bytes
 //
 // It takes the place of the reference's two kernels, mm_gemm_kernel
 // (opengemm/src/mm/kernel.cuh:38-601) and smm_gemm_kernel
@@ -35,7 +36,6 @@ constexpr int CLC_READERS = 6;           // per CTA: producer, warp 1's thread, 
 struct alignas(64) GemmParams {
   CUtensorMap map_x;    // MMA-M side operand, [rows_m, K]
   CUtensorMap map_y;    // MMA-N side operand, [rows_n, K]
-  CUtensorMap map_d;    // output, boxes of 32 rows x 128 bytes (TMA-store epilogue)
   CUtensorMap map_sfx;  // scales of the M side, blocked layout seen as [atoms*2, 256] bytes
   CUtensorMap map_sfy;  // scales of the N side
   void* d;              // output base pointer
@@ -56,7 +56,7 @@ struct alignas(64) GemmParams {
   int acc_slots, acc_stride;   // accumulator ring in tensor memory
   int sf_col, sf_slots, sf_cols;  // scale ring in tensor memory
   int tmem_cols;
-  int epi_tma;            // 1: staging + TMA store; 0: direct global stores
+  int epi_staged;         // 1: rows staged in shared memory, stored as whole 128-byte lines; 0: each thread stores its own row
   int vec_ok;             // direct stores may use 16-byte vectors
   int sf_atoms;           // 512-byte scale atoms per stage per 128-row block
   int sf_yblocks;         // 128-row blocks of N-side scales per tile (1 or 2)
@@ -278,7 +278,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     mbar_init_fence();
     prefetch_tmap(&params.map_x);
     prefetch_tmap(&params.map_y);
-    if (p.epi_tma) prefetch_tmap(&params.map_d);
     if constexpr (SCALED) {
       prefetch_tmap(&params.map_sfx);
       prefetch_tmap(&params.map_sfy);
@@ -476,12 +475,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const uint32_t acc_empty_leader =
         (CTA_GROUP == 2) ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
-    const uint32_t my_buf = epi_base + (warp - 2) * 2 * EPI_BUF_BYTES;
+    const uint32_t my_buf = epi_base + (warp - 2) * EPI_BUF_BYTES;
     constexpr int CHUNK = (OUT_BYTES == 2) ? 64 : 32;  // columns per 128-byte staging row
-    int buf_use = 0;
+    constexpr int UNIT = 16 / OUT_BYTES;               // columns per 16-byte unit of a row
+    // A store instruction of the staged path writes four rows x 128 contiguous
+    // bytes: this lane's row of the four and its 16-byte unit of the eight.
+    const int sub_row = lane >> 3, unit = lane & 7;
     bool touched_memory = false;
     const int tile_n = p.tile_n, rows_m = p.rows_m, rows_n = p.rows_n, ldd = p.ldd;
-    const bool epi_tma = p.epi_tma != 0, transpose_out = p.transpose_out != 0, vec_ok = p.vec_ok != 0;
+    const bool staged = p.epi_staged != 0, transpose_out = p.transpose_out != 0, vec_ok = p.vec_ok != 0;
     uint8_t* const out = static_cast<uint8_t*>(p.d);
     int tile_idx = 0;
     // Stream-K bookkeeping: this warp's region of the partial-sum workspace
@@ -508,7 +510,79 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       const int col0 = t.ni * tile_n;
       const uint32_t acc_tmem = tmem_base + lane_base + slot * p.acc_stride;
 
-      for (int c = 0; c < tile_n && col0 + c < rows_n; c += CHUNK) {
+      // Staged output: each lane writes its row's 128 bytes (32 words `w`, the
+      // first `width` columns valid) into the warp's buffer with the 16-byte
+      // units XOR-swizzled by row, then the warp reads the buffer back four
+      // rows at a time and stores whole 128-byte segments, clipped at the
+      // edges of D.  Plain st.global: nothing to wait for before the buffer
+      // is reused but the warp's own reads.
+      auto store_staged = [&](const uint32_t* w, int c, int width) {
+        const uint32_t rowaddr = my_buf + lane * 128;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (u * UNIT < width)
+            st_shared_v4(rowaddr + ((u ^ (lane & 7)) << 4), w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+        __syncwarp();
+        const int gcol = col0 + c + unit * UNIT;
+        if (unit * UNIT < width && gcol < rows_n) {
+          uint8_t* dst = out + (size_t(row0 + sub_row) * ldd + gcol) * OUT_BYTES;
+          const size_t step = size_t(4) * ldd * OUT_BYTES;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + sub_row;
+            if (row0 + r < rows_m)
+              *reinterpret_cast<uint4*>(dst + i * step) = ld_shared_v4(my_buf + r * 128 + ((unit ^ (r & 7)) << 4));
+          }
+        }
+        __syncwarp();
+      };
+
+      // A 256-wide block-scaled tile leaves tensor memory no room for a second
+      // accumulator, so the MMA warp idles until this one is handed back.  The
+      // hand-back therefore comes as early as possible: the first two 64-column
+      // chunks are stored while the loads of the next chunk are in flight, the
+      // last two are packed to bf16 and held in registers, the accumulator is
+      // released, and only then are the held chunks stored.
+      bool handed_back = false;
+      if constexpr (OUT_BYTES == 2) {
+        if (p.acc_slots == 1 && staged && tile_n == 256 && !contributes && !finishes && row0 < rows_m) {
+          auto pack64 = [](const uint32_t* f, uint32_t* w) {
+#pragma unroll
+            for (int u = 0; u < 32; ++u)
+              w[u] = pack_bf16x2(__uint_as_float(f[2 * u]), __uint_as_float(f[2 * u + 1]));
+          };
+          uint32_t va[64], vb[64], held[64];
+          tmem_ld_32(acc_tmem, va), tmem_ld_32(acc_tmem + 32, va + 32);
+          tmem_ld_wait();
+          tmem_ld_settle_32(va), tmem_ld_settle_32(va + 32);
+          tmem_ld_32(acc_tmem + 64, vb), tmem_ld_32(acc_tmem + 96, vb + 32);
+          pack64(va, held);
+          store_staged(held, 0, 64);
+          tmem_ld_wait();
+          tmem_ld_settle_32(vb), tmem_ld_settle_32(vb + 32);
+          tmem_ld_32(acc_tmem + 128, va), tmem_ld_32(acc_tmem + 160, va + 32);
+          pack64(vb, held);
+          store_staged(held, 64, 64);
+          tmem_ld_wait();
+          tmem_ld_settle_32(va), tmem_ld_settle_32(va + 32);
+          tmem_ld_32(acc_tmem + 192, vb), tmem_ld_32(acc_tmem + 224, vb + 32);
+          pack64(va, held);
+          tmem_ld_wait();
+          tmem_ld_settle_32(vb), tmem_ld_settle_32(vb + 32);
+          pack64(vb, held + 32);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + 8 * slot);
+            else mbar_arrive(bar_acc_empty + 8 * slot);
+          }
+          handed_back = true;
+          store_staged(held, 128, 64);
+          store_staged(held + 32, 192, 64);
+        }
+      }
+
+      for (int c = 0; !handed_back && c < tile_n && col0 + c < rows_n; c += CHUNK) {
         const int width = min(CHUNK, tile_n - c);
         uint32_t v[CHUNK];
         if (width >= 32) tmem_ld_32(acc_tmem + c, v);
@@ -567,35 +641,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           continue;
         }
 
-        if (epi_tma && width == CHUNK && row0 < rows_m) {
-          // Stage 32 rows x 128 bytes with the 128-byte swizzle (16-byte unit
-          // index XOR row%8), then one lane stores the box with TMA, which
-          // clips it at the edges of D.
-          const uint32_t buf = my_buf + (buf_use & 1) * EPI_BUF_BYTES;
-          if (buf_use >= 2) {
-            if (lane == 0) tma_store_wait_read<1>();
-            __syncwarp();
-          }
-          ++buf_use;
-          const uint32_t rowaddr = buf + lane * 128;
+        if (staged && row0 < rows_m) {
+          if constexpr (OUT_BYTES == 4) {
+            store_staged(v, c, width);
+          } else {
+            uint32_t w[32];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            uint32_t w0, w1, w2, w3;
-            if constexpr (OUT_BYTES == 4) {
-              w0 = v[4 * u], w1 = v[4 * u + 1], w2 = v[4 * u + 2], w3 = v[4 * u + 3];
-            } else {
-              w0 = pack_bf16x2(__uint_as_float(v[8 * u]), __uint_as_float(v[8 * u + 1]));
-              w1 = pack_bf16x2(__uint_as_float(v[8 * u + 2]), __uint_as_float(v[8 * u + 3]));
-              w2 = pack_bf16x2(__uint_as_float(v[8 * u + 4]), __uint_as_float(v[8 * u + 5]));
-              w3 = pack_bf16x2(__uint_as_float(v[8 * u + 6]), __uint_as_float(v[8 * u + 7]));
-            }
-            st_shared_v4(rowaddr + ((u ^ (lane & 7)) << 4), w0, w1, w2, w3);
-          }
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&params.map_d, buf, col0 + c, row0);
-            tma_store_commit();
+            for (int u = 0; u < 32; ++u)
+              w[u] = pack_bf16x2(__uint_as_float(v[2 * u]), __uint_as_float(v[2 * u + 1]));
+            store_staged(w, c, width);
           }
         } else if (!transpose_out) {
           if (row < rows_m) {
@@ -660,13 +714,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       // The accumulator slot is in registers or on its way out: hand it back.
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
+      if (lane == 0 && !handed_back) {
         if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + 8 * slot);
         else mbar_arrive(bar_acc_empty + 8 * slot);
       }
     }
-    // Shared memory may be released once the last stores have read it.
-    if (lane == 0) tma_store_wait_read<0>();
   }
 
   // ---------------------------------------------------------------- teardown

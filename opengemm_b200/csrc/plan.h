@@ -104,7 +104,7 @@ struct Plan {
   int tiles_m = 0, tiles_n = 0, num_tiles = 0, group = 1;
   uint32_t idesc = 0;
   int acc_slots = 2, acc_stride = 0, sf_col = 0, sf_slots = 1, sf_cols = 0, tmem_cols = 32;
-  int epi_tma = 0, out_bytes = 4;
+  int epi_staged = 0, out_bytes = 4;
   int sf_atoms = 0, sf_yblocks = 0, k_groups = 0;
   int smem_bytes = 0;
   int x_bits = 0, y_bits = 0;        // global bits per value of the X / Y operand
@@ -115,7 +115,7 @@ struct Plan {
 constexpr int SMEM_LIMIT = 227 * 1024;   // dynamic shared memory a CTA may opt into
 constexpr int SMEM_RESERVE = 1024 + 512; // alignment slack + static barriers
 constexpr int PLAN_MAX_STAGES = 16;
-constexpr int EPI_STAGING_BYTES = 4 * 2 * 32 * 128;  // four warps, two 32x128-byte buffers each
+constexpr int EPI_STAGING_BYTES = 4 * 32 * 128;  // four warps, one buffer of 32 rows x 128 bytes each
 
 inline int round_up(int x, int to) { return (x + to - 1) / to * to; }
 inline int ceil_div(int x, int by) { return (x + by - 1) / by; }
@@ -206,10 +206,9 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
   p.tx_bytes = p.cta_group * (x_tx + y_tx + p.sf_bytes);
 
   p.out_bytes = f->out == OUT_BF16 ? 2 : 4;
-  const int chunk = 128 / p.out_bytes;  // columns per staged row
   const int64_t ldd = g.n;              // C is [m, n] row-major whichever way the MMA runs
-  p.epi_tma = (!g.epi_direct && !p.swap && (ldd * p.out_bytes) % 16 == 0 && p.tile_n % chunk == 0) ? 1 : 0;
-  const int epi_bytes = p.epi_tma ? EPI_STAGING_BYTES : 0;
+  p.epi_staged = (!g.epi_direct && !p.swap && (ldd * p.out_bytes) % 16 == 0) ? 1 : 0;
+  const int epi_bytes = p.epi_staged ? EPI_STAGING_BYTES : 0;
   const int fit = (SMEM_LIMIT - SMEM_RESERVE - epi_bytes) / p.stage_bytes;
   p.stages = std::min(fit, PLAN_MAX_STAGES);
   if (g.stages > 0) p.stages = std::min(p.stages, std::max(2, (int)g.stages));

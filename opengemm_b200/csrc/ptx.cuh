@@ -324,6 +324,21 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Ties every later use of 32 registers that an earlier tcgen05.ld filled to
+// this point of the program.  Placed after tcgen05.wait::ld when other work
+// was scheduled between the load and the wait, it keeps the compiler from
+// reading (or moving) those registers before the wait has made them valid.
+__device__ __forceinline__ void tmem_ld_settle_32(uint32_t* v) {
+  asm volatile(""
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]),
+                 "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]),
+                 "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]),
+                 "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]),
+                 "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+               :
+               : "memory");
+}
+
 // ---- shared-memory matrix descriptors ----------------------------------------
 
 // K-major operand tile whose rows are 128 bytes, 128-byte swizzled: groups of

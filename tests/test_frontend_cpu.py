@@ -124,3 +124,13 @@ def test_shard_of_blocked_scales_is_the_blocked_shard():
             n0, n1 = shard.shard_bounds(n, world, rank)
             part = shard.shard_scales(flat, name, n, k, world, rank).numpy()
             assert np.array_equal(part, ora.to_blocked(raw[n0:n1]))
+
+
+def test_the_shape_suite_lists_the_headline_configurations():
+    from opengemm_b200.configs import load_shapes
+
+    shapes = load_shapes()
+    assert len(shapes) >= 68 and len(set(shapes)) == len(shapes)
+    for shape in [(1024, 1024, 1024), (4096, 4096, 4096), (8192, 8192, 8192), (8192, 28672, 8192), (64, 57344, 8192),
+                  (8192, 1024, 8192), (8192, 3584, 8192), (64, 7168, 8192)]:
+        assert shape in shapes

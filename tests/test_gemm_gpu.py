@@ -63,10 +63,28 @@ VARIANTS = [
 @pytest.mark.parametrize("variant", VARIANTS, ids=lambda v: "-".join(f"{k}{int(v[k])}" for k in v))
 def test_tile_plans(name, variant):
     """Every way of tiling the same product must give the same answer: pair or
-    single CTA, each tile width, swapped operands, direct or TMA-store epilogue."""
+    single CTA, each tile width, swapped operands, direct or staged epilogue."""
     m, n, k = 520, 712, 1152
     case = make_case(name, m, n, k, seed=1)
     assert_parity(case, run_library(case, _config(name, **variant)))
+
+
+@pytest.mark.parametrize("name", ["nvfp4", "mxfp8", "mxfp4"])
+@pytest.mark.parametrize("two", [True, False], ids=["pair", "single"])
+def test_single_accumulator_is_reused_across_tiles(name, two):
+    """A 256-wide block-scaled tile has one accumulator in tensor memory; the
+    epilogue hands it back before its last stores, and every CTA here computes
+    more than one tile, so a hand-back that came too early would corrupt the
+    next tile.  N is ragged: the last tile column is clipped by the stores."""
+    from opengemm_b200 import capi
+
+    m, n, k = 2304, 2568, 1024
+    config = _config(name, use_2cta=two, output_n=256)
+    lib, g = capi.bind(name, m, n, k, config)
+    plan = lib.plan(g, 0)
+    assert plan["acc_slots"] == 1 and plan["tiles"] > plan["grid"] // plan["cta_group"]
+    case = make_case(name, m, n, k, seed=9)
+    assert_parity(case, run_library(case, config))
 
 
 STREAM_K_PLANS = [
