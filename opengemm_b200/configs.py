@@ -100,8 +100,9 @@ def _round_up(x, to):
 # costs less than its share of tiles suggests.
 LOAD_BYTES_PER_CLOCK = 80.0
 STORE_BYTES_PER_CLOCK = 27.0
-DRAIN_CLOCKS = 600.0    # single-accumulator tiles: the MMA warp waits while tensor memory is read out
-TILE_CLOCKS = 400.0     # hand-offs per tile that nothing overlaps
+DRAIN_CLOCKS = 300.0    # single-accumulator tiles: the MMA warp waits while tensor memory is read out
+TILE_CLOCKS = 1200.0    # hand-offs per tile that nothing overlaps
+PAIR_CLOCKS = 400.0     # more of them when two CTAs share a tile (barriers across the pair)
 TRAFFIC_ENERGY = 0.25   # energy of moving a clock's worth of operand bytes, in tensor-pipe clocks
 BOOST_GHZ, CAPPED_GHZ = 1.9, 1.35
 HBM_BYTES_PER_US = 6.5e6
@@ -136,7 +137,7 @@ def modelled_us(name, m, n, k, use_2cta, output_n, swap_ab):
     compute = 2.0 * output_n
     load = ((128 + output_n / cg) * 128 + scale_bytes) / LOAD_BYTES_PER_CLOCK
     store = 128 * output_n * d.out.itemsize / STORE_BYTES_PER_CLOCK
-    extra = TILE_CLOCKS + (DRAIN_CLOCKS if scaled and output_n > 192 else 0.0)
+    extra = TILE_CLOCKS + (PAIR_CLOCKS if use_2cta else 0.0) + (DRAIN_CLOCKS if scaled and output_n > 192 else 0.0)
     tile = max(k_blocks * max(compute, load), store) + extra
     energy = max(k_blocks * (compute + TRAFFIC_ENERGY * load), store) + extra
     path_us = waves * tile / (BOOST_GHZ * 1e3)

@@ -134,3 +134,24 @@ def test_the_shape_suite_lists_the_headline_configurations():
     for shape in [(1024, 1024, 1024), (4096, 4096, 4096), (8192, 8192, 8192), (8192, 28672, 8192), (64, 57344, 8192),
                   (8192, 1024, 8192), (8192, 3584, 8192), (64, 7168, 8192)]:
         assert shape in shapes
+
+
+def test_heuristic_configurations_follow_the_tile_time_model():
+    """Wide pair tiles for long-K compute-bound shapes, single CTAs once the
+    output stores dominate, operand swap for decode shapes; every choice binds."""
+    from opengemm_b200 import capi
+    from opengemm_b200.configs import heuristic_config, load_shapes, modelled_us
+
+    big = heuristic_config("e4m3", 8192, 8192, 8192)
+    assert big["use_2cta"] and big["output_n"] == 256 and not big["swap_ab"]
+    assert not heuristic_config("bf16", 8192, 8192, 32)["use_2cta"]
+    decode = heuristic_config("mxfp4", 64, 57344, 8192)
+    assert decode["swap_ab"] and decode["output_n"] == 64
+    # a narrow tile never models faster than the full-width pair tile on a long-K square
+    assert modelled_us("bf16", 8192, 8192, 8192, True, 64, False) > modelled_us("bf16", 8192, 8192, 8192, True, 256, False)
+    for name in ("bf16", "s8", "e2m3", "nvfp4", "mxfp8", "mxfp4"):
+        for m, n, k in load_shapes():
+            try:
+                capi.bind(name, m, n, k, heuristic_config(name, m, n, k))
+            except RuntimeError as exc:  # only K granularity may refuse a suite shape
+                assert "multiple" in str(exc), (name, m, n, k, str(exc))
