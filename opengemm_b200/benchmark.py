@@ -21,6 +21,7 @@ report no baseline (no CUTLASS comparator is wired in).
 import argparse
 import json
 import math
+import statistics
 import sys
 import time
 from pathlib import Path
@@ -59,14 +60,23 @@ def measure(name, m, n, k, window_ms, tune_missing=False):
     if wrong:
         row["status"] = f"INCORRECT: {wrong}"
         return row
-    us = harness.timed(harness.runner(buffers, bound), window_ms=window_ms)
+    kernel = harness.runner(buffers, bound)
+    baseline, why = harness.baseline_for(buffers, name)
+    # Windows of the two sides alternate, so that clock and temperature drift
+    # on a power-capped GPU falls on both alike; medians of three each.
+    ours, theirs = [], []
+    for _ in range(3):
+        ours.append(harness.timed(kernel, window_ms=window_ms, repeats=1))
+        if baseline:
+            theirs.append(harness.timed(baseline, window_ms=window_ms, repeats=1))
+    us = statistics.median(ours)
     flops = 2.0 * m * n * k
+    plan = bound[0].plan(bound[1])
     row.update(status="ok", us=round(us, 3), tflops=round(flops / us / 1e6, 2),
                gbs=round(harness.iteration_bytes(name, m, n, k) / us / 1e3, 1),
-               tile=f"{bound[0].plan(bound[1])['tile_m']}x{bound[0].plan(bound[1])['tile_n']}")
-    baseline, why = harness.baseline_for(buffers, name)
+               tile=f"{plan['tile_m']}x{plan['tile_n']}")
     if baseline:
-        base = harness.timed(baseline, window_ms=window_ms)
+        base = statistics.median(theirs)
         row.update(baseline_us=round(base, 3), speedup=round(base / us, 3))
     else:
         row["baseline"] = why

@@ -106,7 +106,7 @@ PAIR_CLOCKS = 400.0     # more of them when two CTAs share a tile (barriers acro
 TRAFFIC_ENERGY = 0.25   # energy of moving a clock's worth of operand bytes, in tensor-pipe clocks
 BOOST_GHZ, CAPPED_GHZ = 1.9, 1.35
 HBM_BYTES_PER_US = 6.5e6
-HBM_SATURATING_CTAS = 96.0
+HBM_SATURATING_CTAS = 128.0
 
 
 def _smem_bytes_per_value(name):

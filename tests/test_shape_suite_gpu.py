@@ -18,6 +18,9 @@ pytestmark = pytest.mark.gpu
 NAMES = list(ora.FORMATS)
 SHAPES = configs.load_shapes()
 CASES = [(NAMES[(3 * i + j) % len(NAMES)], shape) for i, shape in enumerate(SHAPES) for j in range(3)]
+# the two large shapes of the reference's own test list (scripts/test.py:23-30), for every format
+for _shape in [(2048, 2048, 2048), (1, 8192, 8192)]:
+    CASES += [(name, _shape) for name in NAMES if (name, _shape) not in CASES]
 SAMPLE = 40
 
 
