@@ -100,6 +100,7 @@ typedef struct {
   int32_t tile_m, tile_n, block_k, stages;
   int32_t swap;      /* operands exchanged: B rows ride the 128-row MMA side */
   int32_t epi_staged; /* epilogue stages rows in shared memory and stores whole 128-byte lines */
+  int32_t epi_tma;    /* ... and they leave by TMA store (32-bit output behind a long K loop) */
   int32_t acc_slots; /* accumulator buffers in tensor memory */
   int32_t tmem_cols, smem_bytes;
   int32_t tiles, grid; /* output tiles; CTAs launched */

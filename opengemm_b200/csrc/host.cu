@@ -309,6 +309,13 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
   if (rc != OG_OK) return rc;
   const bool c_aligned = (reinterpret_cast<uintptr_t>(c) & 15) == 0;
   const int epi_staged = p.epi_staged && c_aligned;
+  const int epi_tma = p.epi_tma && c_aligned;
+  if (epi_tma) {
+    const int type = p.format->out == OUT_S32 ? int(CU_TENSOR_MAP_DATA_TYPE_INT32) : int(CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+    rc = encode_2d(&params.map_d, c, type, uint64_t(g->n), uint64_t(g->m), uint64_t(g->n) * p.out_bytes,
+                   uint32_t(128 / p.out_bytes), 32, CU_TENSOR_MAP_SWIZZLE_128B, 0, "the output");
+    if (rc != OG_OK) return rc;
+  }
   if (p.format->scaled) {
     const uint64_t atoms_x = uint64_t(ceil_div(p.rows_m, 128)) * p.k_groups;
     const uint64_t atoms_y = uint64_t(ceil_div(p.rows_n, 128)) * p.k_groups;
@@ -348,6 +355,7 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
   params.sf_cols = p.sf_cols;
   params.tmem_cols = p.tmem_cols;
   params.epi_staged = epi_staged;
+  params.epi_tma = epi_tma;
   params.vec_ok = (c_aligned && (int64_t(g->n) * p.out_bytes) % 16 == 0) ? 1 : 0;
   params.sf_atoms = p.sf_atoms;
   params.sf_yblocks = p.sf_yblocks;
@@ -456,6 +464,7 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
   out->stages = p.stages;
   out->swap = p.swap;
   out->epi_staged = p.epi_staged;
+  out->epi_tma = p.epi_tma;
   out->acc_slots = p.acc_slots;
   out->tmem_cols = p.tmem_cols;
   out->smem_bytes = p.smem_bytes;
@@ -494,13 +503,13 @@ OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, in
       "\"tile_m\":%d,\"tile_n\":%d,\"block_k\":%d,\"mma_k\":%d,\"k_blocks\":%d,\"stages\":%d,\"x_bytes\":%d,"
       "\"y_bytes\":%d,\"sf_bytes\":%d,\"stage_bytes\":%d,\"tx_bytes\":%d,\"tiles_m\":%d,\"tiles_n\":%d,"
       "\"num_tiles\":%d,\"group\":%d,\"idesc\":%u,\"acc_slots\":%d,\"acc_stride\":%d,\"sf_col\":%d,\"sf_slots\":%d,"
-      "\"sf_cols\":%d,\"tmem_cols\":%d,\"epi_staged\":%d,\"out_bytes\":%d,\"out\":%d,\"sf_atoms\":%d,\"sf_yblocks\":%d,"
+      "\"sf_cols\":%d,\"tmem_cols\":%d,\"epi_staged\":%d,\"epi_tma\":%d,\"out_bytes\":%d,\"out\":%d,\"sf_atoms\":%d,\"sf_yblocks\":%d,"
       "\"k_groups\":%d,\"smem_bytes\":%d,\"x_bits\":%d,\"y_bits\":%d,\"x_map\":%d,\"y_map\":%d,\"l2_promo\":%d,"
       "\"grid\":%d,\"m\":%d,\"n\":%d}",
       int(p.format->scaled), p.variant, p.format->kind, p.cta_group, p.swap, p.rows_m, p.rows_n, p.k, p.tile_m,
       p.tile_n, p.block_k, p.mma_k, p.k_blocks, p.stages, p.x_bytes, p.y_bytes, p.sf_bytes, p.stage_bytes,
       p.tx_bytes, p.tiles_m, p.tiles_n, p.num_tiles, p.group, p.idesc, p.acc_slots, p.acc_stride, p.sf_col,
-      p.sf_slots, p.sf_cols, p.tmem_cols, p.epi_staged, p.out_bytes, p.format->out, p.sf_atoms, p.sf_yblocks,
+      p.sf_slots, p.sf_cols, p.tmem_cols, p.epi_staged, p.epi_tma, p.out_bytes, p.format->out, p.sf_atoms, p.sf_yblocks,
       p.k_groups, p.smem_bytes, p.x_bits, p.y_bits, p.x_map, p.y_map, p.l2_promo, grid, g->m, g->n);
   if (wrote < 0 || wrote >= cap) return fail(OG_ERR_BIND, "the buffer of %d bytes is too small for the description", cap);
   return OG_OK;

@@ -9,7 +9,8 @@
 //   warps 2-5   epilogue: tcgen05.ld the accumulator, convert, and store
 //               either each thread its own row, or through a swizzled
 //               staging buffer per warp from which every store instruction
-//               writes four rows x 128 contiguous bytes
+//               writes four rows x 128 contiguous bytes (or, for 32-bit
+//               output behind a long K loop, a TMA store takes the buffer)
 //
 // It takes the place of the reference's two kernels, mm_gemm_kernel
 // (opengemm/src/mm/kernel.cuh:38-601) and smm_gemm_kernel
@@ -36,6 +37,7 @@ constexpr int CLC_READERS = 6;           // per CTA: producer, warp 1's thread, 
 struct alignas(64) GemmParams {
   CUtensorMap map_x;    // MMA-M side operand, [rows_m, K]
   CUtensorMap map_y;    // MMA-N side operand, [rows_n, K]
+  CUtensorMap map_d;    // output, boxes of 32 rows x 128 bytes (TMA-store epilogue only)
   CUtensorMap map_sfx;  // scales of the M side, blocked layout seen as [atoms*2, 256] bytes
   CUtensorMap map_sfy;  // scales of the N side
   void* d;              // output base pointer
@@ -57,6 +59,7 @@ struct alignas(64) GemmParams {
   int sf_col, sf_slots, sf_cols;  // scale ring in tensor memory
   int tmem_cols;
   int epi_staged;         // 1: rows staged in shared memory, stored as whole 128-byte lines; 0: each thread stores its own row
+  int epi_tma;            // 1 (32-bit output, long K loops): the staged rows leave by TMA store instead of st.global
   int vec_ok;             // direct stores may use 16-byte vectors
   int sf_atoms;           // 512-byte scale atoms per stage per 128-row block
   int sf_yblocks;         // 128-row blocks of N-side scales per tile (1 or 2)
@@ -278,6 +281,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     mbar_init_fence();
     prefetch_tmap(&params.map_x);
     prefetch_tmap(&params.map_y);
+    if (p.epi_tma) prefetch_tmap(&params.map_d);
     if constexpr (SCALED) {
       prefetch_tmap(&params.map_sfx);
       prefetch_tmap(&params.map_sfy);
@@ -475,7 +479,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const uint32_t acc_empty_leader =
         (CTA_GROUP == 2) ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
-    const uint32_t my_buf = epi_base + (warp - 2) * EPI_BUF_BYTES;
+    // One staging buffer per warp; two when they drain by TMA store, which
+    // reads a buffer asynchronously while the next one is filled.
+    const bool tma_out = OUT_BYTES == 4 && p.epi_tma != 0;
+    const uint32_t my_buf = epi_base + (warp - 2) * (tma_out ? 2 : 1) * EPI_BUF_BYTES;
+    int buf_use = 0;
     constexpr int CHUNK = (OUT_BYTES == 2) ? 64 : 32;  // columns per 128-byte staging row
     constexpr int UNIT = 16 / OUT_BYTES;               // columns per 16-byte unit of a row
     // A store instruction of the staged path writes four rows x 128 contiguous
@@ -641,7 +649,30 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           continue;
         }
 
-        if (staged && row0 < rows_m) {
+        if (tma_out && width == CHUNK && row0 < rows_m) {
+          // Long K loops hide the stores entirely, and a TMA store costs the
+          // fewest instructions (and the least power on a capped part): stage
+          // the 32 x 128-byte block, then one lane stores the box, which TMA
+          // clips at the edges of D.  Two buffers alternate.
+          if constexpr (OUT_BYTES == 4) {
+            const uint32_t buf = my_buf + (buf_use & 1) * EPI_BUF_BYTES;
+            if (buf_use >= 2) {
+              if (lane == 0) tma_store_wait_read<1>();
+              __syncwarp();
+            }
+            ++buf_use;
+            const uint32_t rowaddr = buf + lane * 128;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              st_shared_v4(rowaddr + ((u ^ (lane & 7)) << 4), v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&params.map_d, buf, col0 + c, row0);
+              tma_store_commit();
+            }
+          }
+        } else if (staged && row0 < rows_m) {
           if constexpr (OUT_BYTES == 4) {
             store_staged(v, c, width);
           } else {
@@ -719,6 +750,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         else mbar_arrive(bar_acc_empty + 8 * slot);
       }
     }
+    // Shared memory may be released once the last TMA stores have read it.
+    if (tma_out && lane == 0) tma_store_wait_read<0>();
   }
 
   // ---------------------------------------------------------------- teardown

@@ -206,6 +206,13 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
   if (rc != OG_OK) return rc;
   const bool c_aligned = (reinterpret_cast<uintptr_t>(c) & 15) == 0;
   const int epi_staged = p.epi_staged && c_aligned;
+  const int epi_tma = p.epi_tma && c_aligned;
+  if (epi_tma) {
+    const int type = p.format->out == OUT_S32 ? int(CU_TENSOR_MAP_DATA_TYPE_INT32) : int(CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+    rc = encode(&params.map_d, c, type, uint64_t(g->n), uint64_t(g->m), uint64_t(g->n) * p.out_bytes,
+                uint32_t(128 / p.out_bytes), 32, CU_TENSOR_MAP_SWIZZLE_128B, "the output");
+    if (rc != OG_OK) return rc;
+  }
   if (p.format->scaled) {
     const uint64_t atoms_x = uint64_t(ceil_div(p.rows_m, 128)) * p.k_groups;
     const uint64_t atoms_y = uint64_t(ceil_div(p.rows_n, 128)) * p.k_groups;
@@ -245,6 +252,7 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
   params.sf_cols = p.sf_cols;
   params.tmem_cols = p.tmem_cols;
   params.epi_staged = epi_staged;
+  params.epi_tma = epi_tma;
   params.vec_ok = (c_aligned && (int64_t(g->n) * p.out_bytes) % 16 == 0) ? 1 : 0;
   params.sf_atoms = p.sf_atoms;
   params.sf_yblocks = p.sf_yblocks;

@@ -104,7 +104,7 @@ struct Plan {
   int tiles_m = 0, tiles_n = 0, num_tiles = 0, group = 1;
   uint32_t idesc = 0;
   int acc_slots = 2, acc_stride = 0, sf_col = 0, sf_slots = 1, sf_cols = 0, tmem_cols = 32;
-  int epi_staged = 0, out_bytes = 4;
+  int epi_staged = 0, epi_tma = 0, out_bytes = 4;
   int sf_atoms = 0, sf_yblocks = 0, k_groups = 0;
   int smem_bytes = 0;
   int x_bits = 0, y_bits = 0;        // global bits per value of the X / Y operand
@@ -115,7 +115,7 @@ struct Plan {
 constexpr int SMEM_LIMIT = 227 * 1024;   // dynamic shared memory a CTA may opt into
 constexpr int SMEM_RESERVE = 1024 + 512; // alignment slack + static barriers
 constexpr int PLAN_MAX_STAGES = 16;
-constexpr int EPI_STAGING_BYTES = 4 * 32 * 128;  // four warps, one buffer of 32 rows x 128 bytes each
+constexpr int EPI_BUF_BYTES_HOST = 32 * 128;  // one staging buffer: 32 rows of one 128-byte swizzle row
 
 inline int round_up(int x, int to) { return (x + to - 1) / to * to; }
 inline int ceil_div(int x, int by) { return (x + by - 1) / by; }
@@ -208,7 +208,13 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
   p.out_bytes = f->out == OUT_BF16 ? 2 : 4;
   const int64_t ldd = g.n;              // C is [m, n] row-major whichever way the MMA runs
   p.epi_staged = (!g.epi_direct && !p.swap && (ldd * p.out_bytes) % 16 == 0) ? 1 : 0;
-  const int epi_bytes = p.epi_staged ? EPI_STAGING_BYTES : 0;
+  p.tiles_m = ceil_div(p.rows_m, p.tile_m);
+  p.tiles_n = ceil_div(p.rows_n, p.tile_n);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  // 32-bit output behind a long K loop leaves by TMA store (two buffers per
+  // warp); everything else staged leaves by plain stores (one buffer).
+  p.epi_tma = (p.epi_staged && p.out_bytes == 4 && p.k_blocks >= 8 && p.tile_n % 32 == 0) ? 1 : 0;
+  const int epi_bytes = p.epi_staged ? 4 * (p.epi_tma ? 2 : 1) * EPI_BUF_BYTES_HOST : 0;
   const int fit = (SMEM_LIMIT - SMEM_RESERVE - epi_bytes) / p.stage_bytes;
   p.stages = std::min(fit, PLAN_MAX_STAGES);
   if (g.stages > 0) p.stages = std::min(p.stages, std::max(2, (int)g.stages));
@@ -228,9 +234,6 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
     return OG_ERR_NO_KERNEL;
   }
 
-  p.tiles_m = ceil_div(p.rows_m, p.tile_m);
-  p.tiles_n = ceil_div(p.rows_n, p.tile_n);
-  p.num_tiles = p.tiles_m * p.tiles_n;
   p.group = std::max(1, std::min<int>(g.supergroup > 0 ? g.supergroup : 8, p.tiles_n));
   p.l2_promo = g.l2_promo;
 

@@ -29,6 +29,7 @@ from .log import log
 
 MARK = "// opengemm"
 CSRC = Path(__file__).resolve().parent / "csrc"
+OUT_TYPES = {0: "CU_TENSOR_MAP_DATA_TYPE_FLOAT32", 1: "CU_TENSOR_MAP_DATA_TYPE_INT32", 2: "CU_TENSOR_MAP_DATA_TYPE_BFLOAT16"}
 KIND_NAMES = ["KIND_F16", "KIND_TF32", "KIND_I8", "KIND_F8F6F4", "KIND_MXF8F6F4", "KIND_MXF4", "KIND_NVF4"]
 
 # Plan fields the kernel reads that are fixed by (dtype, shape, configuration).
@@ -121,6 +122,10 @@ void launch(const void* a, const void* b, const void* sfa, const void* sfb, void
                         {y_rows}, CU_TENSOR_MAP_SWIZZLE_128B);
     const bool c_aligned = (reinterpret_cast<uintptr_t>(c) & 15) == 0;
     p.epi_staged = ({epi_staged} && c_aligned) ? 1 : 0;
+    p.epi_tma = ({epi_tma} && c_aligned) ? 1 : 0;
+    if (p.epi_tma)
+      ok = ok && tile_map(&p.map_d, c, {out_type}, {n}ull, {m}ull, {n}ull * {out_bytes}, {out_box}, 32,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
     if ({scaled}) {{
       const void* sfx = {swap} ? sfb : sfa;
       const void* sfy = {swap} ? sfa : sfb;
@@ -186,6 +191,7 @@ def emit(name, m, n, k, config, stem):
     values = dict(plan)
     values.update(
         kind=KIND_NAMES[plan["kind"]], smem_attr=227 * 1024 - 1024, y_rows=plan["tile_n"] // plan["cta_group"],
+        out_type=OUT_TYPES[plan["out"]], out_box=128 // plan["out_bytes"],
         atoms_x=-(-plan["rows_m"] // 128) * plan["k_groups"], atoms_y=-(-plan["rows_n"] // 128) * plan["k_groups"],
     )
     if d.impl == "smm":
