@@ -166,8 +166,10 @@ def heuristic_config(name, m, n, k):
     cap = _round_up(rows_n, 16)
     if scaled and cap >= 64:
         cap = _round_up(cap, 64)
-    widths = sorted({w for w in range(step, 257, step) if w <= cap} | ({cap} if cap < step or cap <= 256 and not scaled else set()))
-    widths = [w for w in widths if w <= 256] or [min(cap, 256)]
+    widths = [w for w in range(step, 257, step) if w <= cap]
+    if cap <= 256 and cap not in widths and (not scaled or cap < 64):
+        widths.append(cap)  # one tile spanning all of a narrow N
+    widths.sort()
     best = None
     for two in (True, False):
         if two and rows_m <= 128:
