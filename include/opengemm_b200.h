@@ -94,6 +94,13 @@ OG_API int32_t og_smm_launch(const OgGemm* g, const void* a, const void* b, cons
 
 /* ---- additions with no counterpart in the reference ----------------------- */
 
+/* Output variant: besides the reference's fourteen dtype names, og_mm_bind accepts
+ * "<format>.bf16" for every dense float format ("bf16.bf16", "f16.bf16", "tf32.bf16",
+ * "e4m3.bf16", "e5m2.bf16", "e3m2.bf16", "e2m3.bf16", "e2m1.bf16", "e4m3xe5m2.bf16"):
+ * same operands and tile plans, the f32 accumulator rounded to bfloat16 (nearest
+ * even) on the way out, C a row-major bfloat16 [m, n].  og_mm_kernels / og_mm_kernel
+ * enumerate the reference's formats only. */
+
 /* The native tile plan of a bound GEMM, for tuners and reports. */
 typedef struct {
   int32_t cta_group; /* CTAs per MMA: 1 or 2 */

@@ -12,7 +12,7 @@ import torch
 
 from . import capi
 from .configs import resolve_config
-from .dtypes import DTYPES, dtype_name, extent, k_of, sf_block
+from .dtypes import BF16_OUT, BF16_OUT_SUFFIX, DTYPES, base_name, dtype_name, extent, k_of, lookup, sf_block
 
 _bound = {}  # (dtype name, m, n, k) -> (Library, OgGemm), for the life of the process
 
@@ -20,7 +20,7 @@ _bound = {}  # (dtype name, m, n, k) -> (Library, OgGemm), for the life of the p
 def bind(name, m, n, k, device):
     """Resolve and memoise the kernel for a shape."""
     with torch.cuda.device(device):
-        config = resolve_config(name, m, n, k)
+        config = resolve_config(base_name(name), m, n, k)  # the bf16-output variant runs its format's tile plan
     _bound[(name, m, n, k)] = capi.bind(name, m, n, k, config)
     return _bound[(name, m, n, k)]
 
@@ -75,7 +75,7 @@ def output(d, m, n, out, device):
     return out
 
 
-def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None):
+def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=None):
     """Compute C[M, N] = A[M, K] @ B[N, K].T.
 
     Args:
@@ -87,13 +87,24 @@ def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None):
         out: output to write into instead of allocating one.
         atype: element name for a `uint8` operand: "u8", "e3m2", "e2m3" or "e2m1".
         btype: element name for `b`; defaults to `atype` when the dtypes match.
+        out_dtype: `torch.bfloat16` makes a dense float format round its f32
+            accumulator to bfloat16 on the way out (an addition of this build;
+            the default, None, is the reference's output type).  Implied by a
+            bfloat16 `out`.
 
     Returns:
-        `(M, N)` row-major: float32 for dense formats, int32 for s8 and u8,
-        bfloat16 for block-scaled ones.
+        `(M, N)` row-major: float32 for dense formats (bfloat16 with
+        `out_dtype=torch.bfloat16`), int32 for s8 and u8, bfloat16 for
+        block-scaled ones.
     """
     name = dtype_name(a, b, sfa, atype, btype)
-    d = DTYPES[name]
+    if out_dtype is None and out is not None and out.dtype is torch.bfloat16 and DTYPES[name].out is torch.float32:
+        out_dtype = torch.bfloat16
+    if out_dtype is not None and out_dtype is not DTYPES[name].out:
+        if out_dtype is not torch.bfloat16 or name + BF16_OUT_SUFFIX not in BF16_OUT:
+            raise TypeError(f"{name} writes {DTYPES[name].out}; only dense float formats can write torch.bfloat16 instead")
+        name += BF16_OUT_SUFFIX
+    d = lookup(name)
     m, n, k = a.size(0), b.size(0), k_of(d, a.size(1))
     check_operands(d, m, n, k, a, b, sfa, sfb)
     lib, g = _bound.get((name, m, n, k)) or bind(name, m, n, k, a.device)

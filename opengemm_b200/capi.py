@@ -14,7 +14,7 @@ from ctypes import POINTER, byref, c_char, c_char_p, c_int32, c_void_p
 import torch
 
 from . import build
-from .dtypes import DTYPES
+from .dtypes import lookup
 
 ABI_VERSION = 3
 OG_OK, OG_ERR_BIND, OG_ERR_NO_KERNEL, OG_ERR_TENSORMAP, OG_ERR_LAUNCH, OG_ERR_TIMEOUT = 0, -1, -2, -3, -4, -5
@@ -252,5 +252,5 @@ def library(impl):
 
 def bind(name, m, n, k, config):
     """`(library, OgGemm)` for a configuration on a shape."""
-    lib = library(DTYPES[name].impl)
+    lib = library(lookup(name).impl)
     return lib, lib.bind(name, m, n, k, config)

@@ -24,7 +24,7 @@
 
 namespace og {
 
-// Implemented in kernels_dense.cu (variants 0-7) and kernels_scaled.cu (8-13).
+// Implemented in kernels_dense.cu (variants 0-7 and 14-19) and kernels_scaled.cu (8-13).
 cudaError_t configure_dense(int variant, int smem_bytes);
 cudaError_t configure_scaled(int variant, int smem_bytes);
 cudaError_t launch_dense(int variant, const GemmParams& params, int grid, int smem_bytes,
@@ -33,11 +33,11 @@ cudaError_t launch_scaled(int variant, const GemmParams& params, int grid, int s
                           cudaStream_t stream, bool pdl);
 
 inline cudaError_t configure_variant(int variant, int smem_bytes) {
-  return variant < 8 ? configure_dense(variant, smem_bytes) : configure_scaled(variant, smem_bytes);
+  return (variant < 8 || variant >= 14) ? configure_dense(variant, smem_bytes) : configure_scaled(variant, smem_bytes);
 }
 inline cudaError_t launch_variant(int variant, const GemmParams& params, int grid, int smem_bytes,
                                   cudaStream_t stream, bool pdl) {
-  return variant < 8 ? launch_dense(variant, params, grid, smem_bytes, stream, pdl)
+  return (variant < 8 || variant >= 14) ? launch_dense(variant, params, grid, smem_bytes, stream, pdl)
                      : launch_scaled(variant, params, grid, smem_bytes, stream, pdl);
 }
 

@@ -186,7 +186,7 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
     std::lock_guard<std::mutex> lock(setup_mutex);
     const uint64_t bit = 1ull << p.variant;
     if (!(dev->configured & bit)) {
-      const cudaError_t raised = p.variant < 8 ? configure_dense(p.variant, SMEM_LIMIT - 1024)
+      const cudaError_t raised = (p.variant < 8 || p.variant >= 14) ? configure_dense(p.variant, SMEM_LIMIT - 1024)
                                                : configure_scaled(p.variant, SMEM_LIMIT - 1024);
       if (raised != cudaSuccess) return refuse(OG_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(raised));
       dev->configured |= bit;
@@ -280,7 +280,7 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
     params.partial = reinterpret_cast<float*>(dev->workspace);
     params.flags = reinterpret_cast<int*>(flags);
   }
-  const cudaError_t launched = p.variant < 8 ? launch_dense(p.variant, params, grid, p.smem_bytes, s, false)
+  const cudaError_t launched = (p.variant < 8 || p.variant >= 14) ? launch_dense(p.variant, params, grid, p.smem_bytes, s, false)
                                              : launch_scaled(p.variant, params, grid, p.smem_bytes, s, false);
   if (launched != cudaSuccess) return refuse(OG_ERR_LAUNCH, "kernel launch failed: %s", cudaGetErrorString(launched));
   return OG_OK;

@@ -77,7 +77,20 @@ constexpr Format FORMATS[] = {
     {"nvfp4", true, "e2m1", "e2m1", 6, OUT_BF16, 16, 0},
     {"mxfp8", true, "e4m3", "e4m3", 4, OUT_BF16, 32, 1},
     {"mxfp4", true, "e2m1", "e2m1", 5, OUT_BF16, 32, 1},
+    // Additions with no counterpart in the reference: the dense float formats
+    // with the f32 accumulator rounded to bfloat16 on the way out
+    // ("<format>.bf16"), which halves the bytes of C.
+    {"bf16.bf16", false, "bf16", "bf16", 0, OUT_BF16, 0, 0},
+    {"f16.bf16", false, "f16", "f16", 0, OUT_BF16, 0, 0},
+    {"tf32.bf16", false, "tf32", "tf32", 1, OUT_BF16, 0, 0},
+    {"e4m3.bf16", false, "e4m3", "e4m3", 3, OUT_BF16, 0, 0},
+    {"e5m2.bf16", false, "e5m2", "e5m2", 3, OUT_BF16, 0, 0},
+    {"e3m2.bf16", false, "e3m2", "e3m2", 3, OUT_BF16, 0, 0},
+    {"e2m3.bf16", false, "e2m3", "e2m3", 3, OUT_BF16, 0, 0},
+    {"e2m1.bf16", false, "e2m1", "e2m1", 3, OUT_BF16, 0, 0},
+    {"e4m3xe5m2.bf16", false, "e4m3", "e5m2", 3, OUT_BF16, 0, 0},
 };
+constexpr int NUM_REFERENCE_FORMATS = 14;  // the leading rows are the reference's fourteen
 constexpr int NUM_FORMATS = sizeof(FORMATS) / sizeof(FORMATS[0]);
 
 inline const Element* element(const char* name) {
@@ -95,7 +108,7 @@ inline const Format* format_named(const char (&dtype)[16]) {
 // Everything the launcher needs beyond pointers: filled by make_plan.
 struct Plan {
   const Format* format = nullptr;
-  int variant = -1;  // kind * 2 + (cta_group - 1): which compiled kernel
+  int variant = -1;  // which compiled kernel: kind * 2 + (cta_group - 1); 14 + ... for dense formats with bf16 output
   int cta_group = 1;
   int swap = 0;
   int rows_m = 0, rows_n = 0, k = 0;  // MMA-side extents (after swap)
@@ -171,6 +184,8 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
   p.cta_group = g.use_2cta ? 2 : 1;
   p.swap = g.swap_ab ? 1 : 0;
   p.variant = f->kind * 2 + (p.cta_group - 1);
+  if (!f->scaled && f->out == OUT_BF16)  // kinds 0, 1, 3 (no integer kind) -> 14..19
+    p.variant = 14 + (f->kind == 3 ? 2 : f->kind) * 2 + (p.cta_group - 1);
   const Element* ea = element(f->a);
   const Element* eb = element(f->b);
   const Element* ex = p.swap ? eb : ea;
@@ -263,7 +278,7 @@ inline int menu_rows(bool scaled, MenuRow* rows, int cap) {
   static const int dense_n[] = {16, 32, 64, 96, 128, 160, 192, 224, 256};
   static const int scaled_n[] = {16, 32, 64, 128, 192, 256};
   int count = 0;
-  for (int fi = 0; fi < NUM_FORMATS; ++fi) {
+  for (int fi = 0; fi < NUM_REFERENCE_FORMATS; ++fi) {  // the menu a reference-side tuner walks: its own formats
     if (FORMATS[fi].scaled != scaled) continue;
     for (int two = 0; two < 2; ++two)
       for (int swap = 0; swap < 2; ++swap) {

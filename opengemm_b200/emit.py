@@ -169,6 +169,8 @@ void launch(const void* a, const void* b, const void* sfa, const void* sfb, void
 
 def emit(name, m, n, k, config, stem):
     """`(source, header)` text of the standalone kernel for one configuration."""
+    if name not in DTYPES:
+        raise ValueError(f"standalone kernels are emitted for the fourteen formats {list(DTYPES)}, not {name}")
     d = DTYPES[name]
     lib, g = capi.bind(name, m, n, k, config)
     plan = lib.describe(g)

@@ -455,3 +455,19 @@ def check_north_star(name, got, want):
     excess = np.abs(g - w) - (bf16_ulp(w) + 1e-2 * np.abs(w) + floor)
     ok = bool((excess <= 0).all())
     return ok, float(excess.max()) if excess.size else 0.0
+
+
+def check_bf16_output(got_bits, want_f32):
+    """Acceptance for a dense format whose f32 accumulator is rounded to
+    bfloat16 on the way out (an output variant this build adds; the reference
+    has none, so the rule is stated here): every output within one bfloat16
+    unit in the last place of the float32 reference, plus 2^-20 of the largest
+    |reference| (sums that cancel to nearly zero carry the rounding of their
+    terms, not of their value).  Returns (ok, worst excess in ulps)."""
+    got = bf16_to_f32(np.asarray(got_bits).view(np.uint16)).astype(np.float64)
+    want = np.asarray(want_f32, dtype=np.float64)
+    floor = 2.0**-20 * (float(np.abs(want).max()) if want.size else 0.0)
+    ulp = bf16_ulp(want)
+    excess = (np.abs(got - want) - floor) / ulp
+    bad = ~(excess <= 1.0)
+    return (not bad.any()), float(np.nanmax(excess)) if excess.size else 0.0

@@ -155,3 +155,30 @@ def test_heuristic_configurations_follow_the_tile_time_model():
                 capi.bind(name, m, n, k, heuristic_config(name, m, n, k))
             except RuntimeError as exc:  # only K granularity may refuse a suite shape
                 assert "multiple" in str(exc), (name, m, n, k, str(exc))
+
+
+def test_bf16_output_variants_bind_and_stay_out_of_the_reference_tables():
+    """The "<format>.bf16" names exist for dense float formats only, run their
+    format's tile plan with 2-byte output, and appear neither in DTYPES nor in
+    the kernel menu a reference-side tuner walks."""
+    import opengemm_b200 as og
+    from opengemm_b200 import capi
+    from opengemm_b200.configs import heuristic_config
+    from opengemm_b200.dtypes import BF16_OUT, DTYPES, base_name, lookup
+
+    assert len(DTYPES) == 14 and sorted(BF16_OUT) == sorted(
+        n + ".bf16" for n, d in DTYPES.items() if d.impl == "mm" and d.out is torch.float32)
+    assert base_name("e4m3xe5m2.bf16") == "e4m3xe5m2" and base_name("nvfp4") == "nvfp4"
+    assert lookup("tf32.bf16").out is torch.bfloat16 and lookup("tf32").out is torch.float32
+    for name in BF16_OUT:
+        lib, g = capi.bind(name, 512, 768, 1024, heuristic_config(base_name(name), 512, 768, 1024))
+        described = lib.describe(g)
+        assert described["out_bytes"] == 2 and 14 <= described["variant"] <= 19
+    mm = capi.library("mm")
+    assert all("." not in row["dtype"] for row in mm.kernels())
+    with pytest.raises(TypeError):
+        lookup("s8.bf16")
+    from opengemm_b200 import emit
+
+    with pytest.raises(ValueError):  # standalone kernels are emitted for the fourteen formats only
+        emit.emit("e4m3.bf16", 256, 256, 256, heuristic_config("e4m3", 256, 256, 256), "mm_e4m3_256_256_256")
