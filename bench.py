@@ -375,6 +375,35 @@ def side_configs(torch, device, skip):
         torch.cuda.empty_cache()
     except Exception as exc:
         results["quantize_nvfp4_28672x8192"] = {"error": str(exc)[:160]}
+    # The headline product with C rounded to bfloat16 on the way out (an output
+    # variant of this build; the reference writes float32 only).
+    try:
+        from opengemm_b200 import capi
+        from opengemm_b200.configs import resolve_config
+
+        work = WORKLOADS["c2"]
+        name, m, n, k = work["name"], work["m"], work["n"], work["k"]
+        r = Runner(torch, work, device, seed0=70, max_bytes=2 << 30)
+        lib, g = capi.bind(name + ".bf16", m, n, k, resolve_config(name, m, n, k))
+        outs = [torch.empty((m, n), device=device, dtype=torch.bfloat16) for _ in r.sets]
+        state = {"i": 0}
+
+        def bf16_step():
+            i = state["i"] % r.copies
+            state["i"] += 1
+            a, b, _, _, _ = r.sets[i]
+            lib.launch(g, a, b, None, None, outs[i])
+
+        for _ in range(3):
+            bf16_step()
+        torch.cuda.synchronize()
+        us = min(time_launches(torch, bf16_step, 50) for _ in range(3)) * 1e3 / 50
+        results["c2_bf16_output"] = {"dtype": name + ".bf16", "mnk": [m, n, k], "us": round(us, 2),
+                                     "tflops": round(2.0 * m * n * k / us / 1e6, 1)}
+        del r, outs
+        torch.cuda.empty_cache()
+    except Exception as exc:
+        results["c2_bf16_output"] = {"error": str(exc)[:160]}
     return results
 
 
