@@ -182,3 +182,18 @@ def test_bf16_output_variants_bind_and_stay_out_of_the_reference_tables():
 
     with pytest.raises(ValueError):  # standalone kernels are emitted for the fourteen formats only
         emit.emit("e4m3.bf16", 256, 256, 256, heuristic_config("e4m3", 256, 256, 256), "mm_e4m3_256_256_256")
+
+
+def test_suite_report_summary_counts_and_geometric_mean():
+    from opengemm_b200.benchmark import summarise
+
+    rows = [
+        {"dtype": "bf16", "status": "ok", "speedup": 2.0},
+        {"dtype": "bf16", "status": "ok", "speedup": 0.5},
+        {"dtype": "bf16", "status": "skipped: K too small"},
+        {"dtype": "bf16", "status": "INCORRECT: mismatch"},
+        {"dtype": "mxfp4", "status": "ok"},  # no library kernel to compare with
+    ]
+    out = summarise(rows)
+    assert out["bf16"] == {"measured": 2, "skipped": 1, "incorrect": 1, "geomean_speedup": 1.0, "below_0.95": 1}
+    assert out["mxfp4"]["geomean_speedup"] is None and out["mxfp4"]["measured"] == 1
