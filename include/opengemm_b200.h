@@ -127,6 +127,14 @@ OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void
                                       const void* sfa, const void* sfb, void* c, int32_t device,
                                       void* stream, int32_t* status);
 
+/* Launch like og_mm_launch / og_smm_launch (chosen by g->dtype) with every output
+ * multiplied by `alpha` in float32 before it is stored (the product of per-tensor
+ * dequantisation scales of fp8 / fp4 operands, for instance).  Float formats only:
+ * s8 and u8 answer OG_ERR_LAUNCH. */
+OG_API int32_t og_b200_launch_alpha(const OgGemm* g, const void* a, const void* b,
+                                    const void* sfa, const void* sfb, void* c, int32_t device,
+                                    void* stream, float alpha);
+
 /* The complete tile plan of a bound `g` for a device of `sm_count` SMs, as one JSON
  * object of integers written to `out` (what the standalone-kernel emitter bakes
  * into the code it writes).  Needs no GPU. */

@@ -75,7 +75,7 @@ def output(d, m, n, out, device):
     return out
 
 
-def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=None):
+def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=None, alpha=None):
     """Compute C[M, N] = A[M, K] @ B[N, K].T.
 
     Args:
@@ -91,6 +91,9 @@ def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=N
             accumulator to bfloat16 on the way out (an addition of this build;
             the default, None, is the reference's output type).  Implied by a
             bfloat16 `out`.
+        alpha: a Python float every output is multiplied by (in float32) before
+            it is stored, e.g. the product of per-tensor scales of fp8 operands
+            (an addition of this build; float formats only).
 
     Returns:
         `(M, N)` row-major: float32 for dense formats (bfloat16 with
@@ -109,5 +112,10 @@ def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=N
     check_operands(d, m, n, k, a, b, sfa, sfb)
     lib, g = _bound.get((name, m, n, k)) or bind(name, m, n, k, a.device)
     out = output(d, m, n, out, a.device)
-    lib.launch(g, a, b, sfa, sfb, out)
+    if alpha is None:
+        lib.launch(g, a, b, sfa, sfb, out)
+    else:
+        if d.out is torch.int32:
+            raise TypeError(f"{name} accumulates integers exactly: its output cannot be scaled")
+        lib.launch_alpha(g, a, b, sfa, sfb, out, alpha)
     return out

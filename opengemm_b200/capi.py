@@ -128,6 +128,9 @@ class Library:
         self._plan = getattr(lib, "og_b200_plan", None)
         if self._plan is not None:
             self._plan.restype, self._plan.argtypes = c_int32, [POINTER(OgGemm), c_int32, POINTER(OgPlan)]
+            self._alpha = lib.og_b200_launch_alpha
+            self._alpha.restype = c_int32
+            self._alpha.argtypes = [POINTER(OgGemm)] + [c_void_p] * 5 + [c_int32, c_void_p, ctypes.c_float]
             self._checked = lib.og_b200_launch_checked
             self._checked.restype = c_int32
             self._checked.argtypes = [POINTER(OgGemm)] + [c_void_p] * 5 + [c_int32, c_void_p, c_void_p]
@@ -201,6 +204,17 @@ class Library:
             byref(g), a.data_ptr(), b.data_ptr(),
             0 if sfa is None else sfa.data_ptr(), 0 if sfb is None else sfb.data_ptr(),
             out.data_ptr(), device, raw_stream(device), status_word.data_ptr(),
+        )
+        if status != OG_OK:
+            raise RuntimeError(self.error())
+
+    def launch_alpha(self, g, a, b, sfa, sfb, out, alpha):
+        """Like `launch`, every output multiplied by `alpha` in float32 before it is stored."""
+        device = a.get_device()
+        status = self._alpha(
+            byref(g), a.data_ptr(), b.data_ptr(),
+            0 if sfa is None else sfa.data_ptr(), 0 if sfb is None else sfb.data_ptr(),
+            out.data_ptr(), device, raw_stream(device), float(alpha),
         )
         if status != OG_OK:
             raise RuntimeError(self.error())

@@ -270,7 +270,7 @@ struct PlanMemo {
 thread_local PlanMemo plan_memo;
 
 int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, const void* sfb,
-                void* c, int device, void* stream, int* status_word, int want_scaled) {
+                void* c, int device, void* stream, int* status_word, int want_scaled, const float* alpha = nullptr) {
   if (!g) return fail(OG_ERR_LAUNCH, "null OgGemm");
   if (!plan_memo.valid || std::memcmp(&plan_memo.key, g, sizeof(OgGemm)) != 0) {
     char why[256];
@@ -288,6 +288,8 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
   if (!a || !b || !c) return fail(OG_ERR_LAUNCH, "a, b and c must be device pointers, got null");
   if (p.format->scaled && (!sfa || !sfb))
     return fail(OG_ERR_LAUNCH, "a block-scaled format takes both sfa and sfb");
+  if (alpha && p.format->out == OUT_S32)
+    return fail(OG_ERR_LAUNCH, "dtype %.16s accumulates integers exactly: its output cannot be scaled", g->dtype);
   const int followed = follow_device(device);
   if (followed != OG_OK) return followed;
   const int configured = ensure_configured(device, p.variant, p.smem_bytes);
@@ -360,6 +362,10 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
   params.sf_atoms = p.sf_atoms;
   params.sf_yblocks = p.sf_yblocks;
   params.k_groups = p.k_groups;
+  if (alpha) {
+    params.scale_out = 1;
+    params.alpha = *alpha;
+  }
   static const bool pdl_enabled = [] { const char* e = getenv("OPENGEMM_PDL"); return !(e && e[0] == '0'); }();
   params.pdl = pdl_enabled ? (independent_inputs.load(std::memory_order_relaxed) ? 2 : 1) : 0;
 
@@ -488,6 +494,11 @@ OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void
                                       const void* sfa, const void* sfb, void* c, int32_t device,
                                       void* stream, int32_t* status) {
   return launch_impl(g, a, b, sfa, sfb, c, device, stream, status, -1);
+}
+
+OG_API int32_t og_b200_launch_alpha(const OgGemm* g, const void* a, const void* b, const void* sfa,
+                                    const void* sfb, void* c, int32_t device, void* stream, float alpha) {
+  return launch_impl(g, a, b, sfa, sfb, c, device, stream, nullptr, -1, &alpha);
 }
 
 OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, int32_t cap) {

@@ -72,6 +72,8 @@ struct alignas(64) GemmParams {
   int stream_k;
   int sk_clusters;        // clusters that share the partial wave's units (the rest only run whole tiles)
   int acc_int;            // accumulators are s32 (partials add as integers)
+  int scale_out;          // 1: float accumulators are multiplied by `alpha` before they are stored
+  float alpha;
   int epoch;              // this launch's tag in `flags` (never 0)
   float* partial;         // per epilogue warp: 32 rows x 256 columns of f32 partial sums
   int* flags;             // per epilogue warp: epoch of the partial it last published
@@ -493,6 +495,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     const int tile_n = p.tile_n, rows_m = p.rows_m, rows_n = p.rows_n, ldd = p.ldd;
     const bool staged = p.epi_staged != 0, transpose_out = p.transpose_out != 0, vec_ok = p.vec_ok != 0;
     uint8_t* const out = static_cast<uint8_t*>(p.d);
+    const bool scale_out = p.scale_out != 0;  // scaled output takes the general loop below
+    const float alpha = p.alpha;
     int tile_idx = 0;
     // Stream-K bookkeeping: this warp's region of the partial-sum workspace
     // and its neighbour's (the same warp of the next cluster).
@@ -553,7 +557,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       // released, and only then are the held chunks stored.
       bool handed_back = false;
       if constexpr (OUT_BYTES == 2) {
-        if (p.acc_slots == 1 && staged && tile_n == 256 && !contributes && !finishes && row0 < rows_m) {
+        if (p.acc_slots == 1 && staged && tile_n == 256 && !contributes && !finishes && !scale_out && row0 < rows_m) {
           auto pack64 = [](const uint32_t* f, uint32_t* w) {
 #pragma unroll
             for (int u = 0; u < 32; ++u)
@@ -637,6 +641,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
               }
             }
           }
+        }
+        if (scale_out && !contributes) {  // the finished sum, scaled once; partial sums travel unscaled
+#pragma unroll
+          for (int j = 0; j < CHUNK; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
         }
         if (contributes) {
           // Raw accumulators, 16 bytes per lane per vector so a warp writes 512
