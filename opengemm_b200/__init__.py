@@ -7,6 +7,10 @@
     og.run_kernel("k.cu", a, b)            # compile and run it
 
 The public names are those of the reference package (opengemm/__init__.py:10-28).
+Additions of this build, all optional: `og.gemm(..., out_dtype=torch.bfloat16)`
+and `og.gemm(..., alpha=0.5)` (output variants), `og.quantize_blocked` (values ->
+packed data + blocked scales in one kernel), `python -m opengemm_b200.tune`
+and `python -m opengemm_b200.benchmark` (tuner and suite runner).
 """
 
 from .api import gemm
