@@ -44,7 +44,7 @@ def raw(t):
 
 def main():
     parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="a checkout of aramesh10/OpenGEMM (its Python is imported on the CPU)")
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
 
