@@ -9,6 +9,7 @@ from ctypes import byref
 from pathlib import Path
 
 import pytest
+import torch
 
 from opengemm_b200 import capi
 from opengemm_b200.configs import heuristic_config
@@ -104,3 +105,36 @@ def test_plan_of_the_baseline_configurations():
         assert plan["grid"] <= 148 and plan["tiles"] >= 1
         if m <= 64:
             assert plan["swap"] == 1  # small M rides the MMA's N side
+
+
+def test_plan_invariants_over_the_shape_suite():
+    """For every format over every suite shape, the plan of the configuration
+    gemm() would pick respects the hardware budget: shared memory within the
+    227 KiB opt-in limit, tensor memory within 512 columns, at least two ring
+    stages, accumulator and scale slots inside the allocation, and a TMA-store
+    epilogue only on top of the staged one with 4-byte output."""
+    from opengemm_b200 import capi
+    from opengemm_b200.configs import heuristic_config, load_shapes
+    from opengemm_b200.dtypes import BF16_OUT, DTYPES, base_name
+
+    checked = 0
+    for name in list(DTYPES) + ["e4m3.bf16", "bf16.bf16"]:
+        for m, n, k in load_shapes():
+            try:
+                lib, g = capi.bind(name, m, n, k, heuristic_config(base_name(name), m, n, k))
+            except RuntimeError as exc:
+                assert "multiple" in str(exc)
+                continue
+            p = lib.describe(g)
+            assert p["smem_bytes"] <= 227 * 1024 and p["stages"] >= 2
+            assert p["tmem_cols"] <= 512 and p["tmem_cols"] & (p["tmem_cols"] - 1) == 0
+            assert p["sf_col"] + p["sf_slots"] * p["sf_cols"] <= p["tmem_cols"]
+            assert p["acc_slots"] * p["acc_stride"] <= p["sf_col"] or p["sf_cols"] == 0
+            assert p["stages"] * p["stage_bytes"] < p["smem_bytes"]
+            assert p["tile_n"] % 16 == 0 and 16 <= p["tile_n"] <= 256
+            assert p["num_tiles"] == p["tiles_m"] * p["tiles_n"] and 1 <= p["grid"] <= 148
+            if p["epi_tma"]:
+                assert p["epi_staged"] and p["out_bytes"] == 4 and p["tile_n"] % 32 == 0
+            assert p["out_bytes"] == (2 if (name in BF16_OUT or DTYPES[base_name(name)].out is torch.bfloat16) else 4)
+            checked += 1
+    assert checked > 1000
