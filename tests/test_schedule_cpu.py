@@ -63,3 +63,40 @@ def test_schedule_covers_every_unit_once_and_pairs_finishers_with_contributors(t
                 found = sharers_found_by_finisher(c, tile, clusters, k_blocks, static_tiles, total)
                 contributors = [j for j, other in enumerate(work) for t, a, _ in other if t == tile and a > 0]
                 assert found == contributors
+
+
+def test_staged_epilogue_addressing_is_a_bijection_without_bank_conflicts():
+    """Python model of the staged output path of the kernel's epilogue
+    (store_staged in csrc/kernel.cuh): lane L writes its row's eight 16-byte
+    units to row L of a 32 x 128-byte buffer at unit u ^ (L % 8); the warp then
+    reads row r = 4 i + L // 8, unit L % 8 back from unit (L % 8) ^ (r % 8).
+    Every (row, unit) must be written once, read once, and come back as the
+    unit it was written as; and the eight lanes that share a shared-memory
+    wavefront (a quarter warp moves 8 x 16 bytes = 128 bytes = all 32 banks)
+    must touch eight different 16-byte bank groups."""
+    buffer = {}
+    for lane in range(32):
+        for u in range(8):
+            address = lane * 128 + ((u ^ (lane & 7)) << 4)
+            assert address not in buffer
+            buffer[address] = (lane, u)  # row, logical unit
+    assert len(buffer) == 256
+    for u in range(8):  # one st.shared.v4 per unit index: quarter warps of eight lanes
+        for quarter in range(4):
+            groups = {((lane * 128 + ((u ^ (lane & 7)) << 4)) >> 4) % 8 for lane in range(8 * quarter, 8 * quarter + 8)}
+            assert len(groups) == 8
+    seen = set()
+    for i in range(8):
+        for lane in range(32):
+            sub_row, unit = lane >> 3, lane & 7
+            r = 4 * i + sub_row
+            row, logical = buffer[r * 128 + ((unit ^ (r & 7)) << 4)]
+            assert (row, logical) == (r, unit)  # the 16 bytes this lane stores belong to row r, columns of `unit`
+            seen.add((r, unit))
+        for quarter in range(4):  # reads: the same no-conflict property
+            groups = set()
+            for lane in range(8 * quarter, 8 * quarter + 8):
+                r = 4 * i + (lane >> 3)
+                groups.add(((r * 128 + (((lane & 7) ^ (r & 7)) << 4)) >> 4) % 8)
+            assert len(groups) == 8
+    assert len(seen) == 256
