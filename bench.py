@@ -57,7 +57,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 # dram bytes (read + write) of one launch of the dominant kernel in this
 # benchmark's own rotation of buffers, from the ncu captures summarised under
 # profiles/; None where no capture is committed.
-NCU_TRAFFIC_BYTES = {"c2": 53.2e6, "c5": 256.1e6, "c4s": 95.5e6, "c1": 4.2e6, "c3s": 81.0e6}
+NCU_TRAFFIC_BYTES = {"c2": 52.3e6, "c5": 256.1e6, "c4s": 95.5e6, "c1": 4.2e6, "c3s": 81.0e6}
 
 
 def measured_peaks():
