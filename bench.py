@@ -1,25 +1,32 @@
 #!/usr/bin/env python3
 """Benchmark of the GEMM hot path on B200: one JSON line on stdout.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c4]
 
-Workload (N = 1): the fp8 configuration the headline metric is quoted on,
-e4m3 x e4m3 -> f32, M = N = K = 4096, operands iid N(0,1)*16 clamped to +-448
-and cast to float8_e4m3fn.  One step = one GEMM call on the next of several
-operand sets (rotated so no step reads what its predecessor left in L2).
-With N > 1 ranks (one per GPU, launched by torch.distributed.run) every rank
-owns one 4096-column shard of B and C of an N-sharded GEMM with global
-N = 4096 * ranks: no collective on the data path, weak scaling.
+Workload: the largest single-GPU configuration of the baseline, the nvfp4
+block-scaled GEMM M = 8192, N = 28672, K = 8192 -> bf16 (operands from
+N(0,1), scale = amax/6 as ue4m3 per 16 values).  One step = one GEMM call on
+the next of several operand sets (rotated so no step reads what its
+predecessor left in L2).  With N > 1 ranks (one per GPU, launched by
+torch.distributed.run) the same GEMM is N-sharded: rank r owns rows
+shard_bounds(N, ranks, r) of B, of B's scales and the matching columns of C;
+A and its scales are replicated; no collective is on the data path.  The job
+is the whole GEMM, so scaling is strong: `value` = 2*M*N*K / the slowest
+rank's time per step.
 
 `value` times the kernel through the C ABI with operands resident in HBM;
 `e2e` times `opengemm_b200.gemm` fed from pinned host memory, with the
-host->device copy of A and B and the device->host copy of C inside the timed
-region every step.  `--impl reference` times the reference's CPU path (its
-correctness oracle, a float32 matmul of the upcast operands) on the host
-cores through the numpy port under oracle/.
+host->device copies of the rank's operands and the device->host copy of its
+part of C inside the timed region every step.  Before any timing the first
+operand set's output is checked against the CPU oracle on sampled rows and
+columns; a miss ends the run with a non-zero exit code.  `--impl reference`
+times the reference's CPU path (its correctness oracle, a float32 matmul of
+the dequantised operands) on the host cores through the numpy port under
+oracle/.
 """
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -27,12 +34,13 @@ import subprocess
 import sys
 import threading
 import time
+from collections import namedtuple
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# The five configurations of the baseline; "c2" is the headline the default run measures.
+# The five configurations of the baseline (and the mixed-fp8 variant of the second).
 WORKLOADS = {
     "c1": {"name": "bf16", "m": 1024, "n": 1024, "k": 1024, "what": "bf16 -> f32 GEMM M=N=K=1024, N(0,1)"},
     "c2": {"name": "e4m3", "m": 4096, "n": 4096, "k": 4096,
@@ -44,20 +52,27 @@ WORKLOADS = {
            "what": "nvfp4 block-scaled GEMM 8192x28672x8192 -> bf16, N(0,1), scale = amax/6 as ue4m3 per 16"},
     "c5": {"name": "mxfp4", "m": 64, "n": 57344, "k": 8192,
            "what": "mxfp4 block-scaled decode GEMM 64x57344x8192 -> bf16, N(0,1), scale = 2^floor(log2(amax/6)) per 32"},
-    # the per-GPU shards of c3 / c4 / c5 when N is split over eight GPUs
-    "c3s": {"name": "s8", "m": 8192, "n": 1024, "k": 8192, "what": "s8 GEMM 8192x1024x8192 (one eighth of c3's N)"},
-    "c4s": {"name": "nvfp4", "m": 8192, "n": 3584, "k": 8192, "what": "nvfp4 GEMM 8192x3584x8192 (one eighth of c4's N)"},
-    "c5s": {"name": "mxfp4", "m": 64, "n": 7168, "k": 8192, "what": "mxfp4 decode GEMM 64x7168x8192 (one eighth of c5's N)"},
 }
+HEADLINE = "c4"
+SHARDED = ("c3", "c4", "c5")  # the configurations the baseline shards along N
 L2_BYTES = 126 * 2**20
+SM_COUNT = 148
 # Dense tensor-core peaks by format relative to bf16 (nominal bf16 2250 TFLOP/s):
 # fp8 / int8 run at twice, fp4 at four times the bf16 rate.
 RATE_VS_BF16 = {"bf16": 1.0, "e4m3": 2.0, "e4m3xe5m2": 2.0, "s8": 2.0, "nvfp4": 4.0, "mxfp4": 4.0}
 NOMINAL_BF16_TFLOPS = 2250.0
 # dram bytes (read + write) of one launch of the dominant kernel in this
 # benchmark's own rotation of buffers, from the ncu captures summarised under
-# profiles/; None where no capture is committed.
-NCU_TRAFFIC_BYTES = {"c2": 52.3e6, "c5": 256.1e6, "c4s": 95.5e6, "c1": 4.2e6, "c3s": 81.0e6}
+# profiles/, keyed by (format, m, n, k); None where no capture is committed.
+NCU_TRAFFIC_BYTES = {
+    ("e4m3", 4096, 4096, 4096): 52.3e6,
+    ("mxfp4", 64, 57344, 8192): 256.1e6,
+    ("nvfp4", 8192, 3584, 8192): 95.5e6,
+    ("bf16", 1024, 1024, 1024): 4.2e6,
+    ("s8", 8192, 1024, 8192): 81.0e6,
+}
+
+Operands = namedtuple("Operands", "a b sfa sfb sfa_raw sfb_raw")
 
 
 def measured_peaks():
@@ -120,7 +135,7 @@ def quantize_fp4(torch, x, block, power_of_two):
     """Block-scaled e2m1 as the baseline's configurations state it: per `block`
     values along K, scale = amax/6 rounded to ue4m3, or 2^floor(log2(amax/6)) as
     ue8m0 (values beyond +-6 x scale saturate); value/scale to the nearest e2m1,
-    two per byte, low nibble first.  Returns (packed, blocked scales)."""
+    two per byte, low nibble first.  Returns (packed, blocked scales, row-major scales)."""
     from opengemm_b200.quant import pack, to_blocked
 
     rows, k = x.shape
@@ -131,34 +146,105 @@ def quantize_fp4(torch, x, block, power_of_two):
     else:
         stored = scale.squeeze(-1).to(torch.float8_e4m3fn)
     q = (groups / stored.float().clamp(min=2.0**-126).unsqueeze(-1)).reshape(rows, k).clamp(-6.0, 6.0)
-    return pack(q, "e2m1").view(torch.float4_e2m1fn_x2), to_blocked(stored)
+    return pack(q, "e2m1").view(torch.float4_e2m1fn_x2), to_blocked(stored), stored
 
 
-def make_operands(torch, name, m, n, k, seed, device):
-    """One operand set `(a, b, sfa, sfb)` in the value distribution the baseline
-    names for this format, generated on `device` from a seeded generator."""
+def make_operands(torch, name, m, n, k, seed, device, seed_b=None):
+    """One operand set in the value distribution the baseline names for this
+    format, generated on `device` from seeded generators: A from `seed`, B
+    from `seed_b` (default: the same generator, after A).  Returns `Operands`;
+    the scale fields are None for dense formats, `sf*_raw` are the row-major
+    `[rows, K/block]` scales the blocked buffers were built from."""
     g = torch.Generator(device=device).manual_seed(seed)
+    gb = g if seed_b is None else torch.Generator(device=device).manual_seed(seed_b)
     if name == "s8":
         a = torch.randint(-128, 128, (m, k), device=device, dtype=torch.int8, generator=g)
-        b = torch.randint(-128, 128, (n, k), device=device, dtype=torch.int8, generator=g)
-        return a, b, None, None
+        b = torch.randint(-128, 128, (n, k), device=device, dtype=torch.int8, generator=gb)
+        return Operands(a, b, None, None, None, None)
     a = torch.randn((m, k), device=device, generator=g)
-    b = torch.randn((n, k), device=device, generator=g)
+    b = torch.randn((n, k), device=device, generator=gb)
     if name == "bf16":
-        return a.to(torch.bfloat16), b.to(torch.bfloat16), None, None
+        return Operands(a.to(torch.bfloat16), b.to(torch.bfloat16), None, None, None, None)
     if name == "e4m3":
-        return ((a * 16).clamp(-448, 448).to(torch.float8_e4m3fn),
-                (b * 16).clamp(-448, 448).to(torch.float8_e4m3fn), None, None)
+        return Operands((a * 16).clamp(-448, 448).to(torch.float8_e4m3fn),
+                        (b * 16).clamp(-448, 448).to(torch.float8_e4m3fn), None, None, None, None)
     if name == "e4m3xe5m2":
-        return ((a * 16).clamp(-448, 448).to(torch.float8_e4m3fn),
-                (b * 64).clamp(-57344, 57344).to(torch.float8_e5m2), None, None)
+        return Operands((a * 16).clamp(-448, 448).to(torch.float8_e4m3fn),
+                        (b * 64).clamp(-57344, 57344).to(torch.float8_e5m2), None, None, None, None)
     if name in ("nvfp4", "mxfp4"):
         block, pow2 = (16, False) if name == "nvfp4" else (32, True)
-        qa, sfa = quantize_fp4(torch, a, block, pow2)
+        qa, sfa, raw_a = quantize_fp4(torch, a, block, pow2)
         del a
-        qb, sfb = quantize_fp4(torch, b, block, pow2)
-        return qa, qb, sfa, sfb
+        qb, sfb, raw_b = quantize_fp4(torch, b, block, pow2)
+        return Operands(qa, qb, sfa, sfb, raw_a, raw_b)
     raise KeyError(name)
+
+
+# ---- the parity gate: sampled rows and columns against the CPU oracle -----------
+
+SAMPLE = 40
+
+
+def sample_indices(extent, rng, count=SAMPLE):
+    """Up to `count` indices: both ends, both sides of every 128 / 256 seam near
+    the ends and the middle, the rest random."""
+    seams = [0, extent - 1]
+    for at in (128, 192, 256, extent // 2 // 128 * 128, (extent - 1) // 256 * 256):
+        seams += [at - 1, at]
+    picks = [i for i in dict.fromkeys(seams) if 0 <= i < extent]
+    spare = count - len(picks)
+    if spare > 0 and extent > len(picks):
+        picks += list(rng.choice(extent, size=min(spare, extent), replace=False))
+    return sorted(set(int(i) for i in picks))[:count]
+
+
+def raw_rows(torch, t, rows):
+    """Selected rows of a device tensor as the storage-typed numpy array the oracle reads."""
+    import numpy as np
+
+    index = torch.as_tensor(rows, device=t.device)
+    if t.dtype in (torch.float32, torch.int8, torch.uint8):
+        return t[index].cpu().numpy()
+    if t.dtype in (torch.bfloat16, torch.float16):
+        return t.view(torch.int16)[index].cpu().numpy().view(np.uint16)
+    return t.view(torch.uint8)[index].cpu().numpy()  # fp8 codes, packed fp4 pairs, scale bytes
+
+
+def sampled_oracle_check(torch, name, k, ops, out, seed=0):
+    """Recompute a sample of output rows x columns of `out` on the CPU oracle
+    from the matching rows of A and B (exact for a product whose entries
+    depend on one row of each operand) and apply both acceptance rules:
+    the reference's assert_close tolerances and the stricter stated bound
+    (bit-exact s32; max|x-ref|/max|ref| <= 1e-3 for f32 output; 1 bf16 ulp +
+    1e-2 relative for block-scaled output).  Returns a dict for the JSON line."""
+    import numpy as np
+    from oracle import opengemm_oracle as ora
+
+    m, n = out.shape
+    rng = np.random.default_rng(seed + m * 31 + n * 17 + k)
+    rows, cols = sample_indices(m, rng), sample_indices(n, rng)
+    scaled = ops.sfa_raw is not None
+    want = ora.reference(name, raw_rows(torch, ops.a, rows), raw_rows(torch, ops.b, cols),
+                         raw_rows(torch, ops.sfa_raw, rows) if scaled else None,
+                         raw_rows(torch, ops.sfb_raw, cols) if scaled else None)
+    picked = out[torch.as_tensor(rows, device=out.device)][:, torch.as_tensor(cols, device=out.device)].contiguous()
+    got = picked.view(torch.int16).cpu().numpy().view(np.uint16) if out.dtype is torch.bfloat16 else picked.cpu().numpy()
+    close, worst = ora.check_close(name, k, got, want)
+    strict, figure = ora.check_north_star(name, got, want)
+    g, w = ora.as_float(name, got), ora.as_float(name, want)
+    scale = max(float(np.abs(w).max()), 1e-30)
+    result = {"checked": True, "ok": bool(close and strict), "samples": int(got.size),
+              "max_rel": float(np.abs(g - w).max() / scale),
+              "rule": "sampled rows x columns against the CPU oracle: the reference's assert_close tolerance and "
+                      + ("bit-exact s32" if out.dtype is torch.int32 else
+                         "max|x-ref|/max|ref| <= 1e-3" if out.dtype is torch.float32 else
+                         "|x-ref| <= 1 bf16 ulp + 1e-2 |ref|")}
+    if out.dtype is torch.bfloat16:
+        result["outputs_needing_the_cancellation_floor"] = int(ora.north_star_floor_users(name, got, want))
+    if not result["ok"]:
+        result["worst_excess"] = float(worst)
+        result["strict_figure"] = float(figure)
+    return result
 
 
 def algorithmic_bytes(name, m, n, k):
@@ -212,10 +298,6 @@ def use_all_host_threads():
         return 1
 
 
-def host_threads():
-    return use_all_host_threads()
-
-
 def cpu_sample(name, m, n, k, budget_s):
     """Size and time a bounded sample of the workload on the CPU oracle:
     `rows` rows of A against `cols` rows of B (all of K), sized from a probe so
@@ -243,6 +325,17 @@ def unit_of(work):
     return ("GB/s", "hbm_gbs") if work["name"] == "mxfp4" and work["m"] <= 128 else ("TFLOP/s", "tflops")
 
 
+def config_of(work, world):
+    """The `config` object of the JSON line; the same for both arms."""
+    return {
+        "workload": work["what"],
+        "m": work["m"], "n": work["n"], "k": work["k"],
+        "parallelism": f"nshard{world}" if world > 1 else "1 GPU",
+        "sharding": "B, its scales and C split along N on 128-row boundaries, A replicated; no collective",
+        "l2": "inputs larger than L2: the GPU arm rotates operand/output sets past 2 x 126 MiB between steps",
+    }
+
+
 def run_reference(args):
     """The reference arm: the reference's CPU path (its oracle) on the host
     cores, through the numpy port, on a bounded sample per step.  Rank 0 only."""
@@ -250,6 +343,7 @@ def run_reference(args):
         return
     work = WORKLOADS[args.workload]
     name, m, n, k = work["name"], work["m"], work["n"], work["k"]
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     budget = max(0.05, min(2.0, 150.0 / max(args.steps + args.warmup, 1)))
     _, rows, cols, runner = cpu_sample(name, m, n, k, budget)
     for _ in range(args.warmup):
@@ -263,14 +357,15 @@ def run_reference(args):
         value = algorithmic_bytes_np(name, rows, cols, k) * args.steps / seconds / 1e9
     else:
         value = 2.0 * rows * cols * k * args.steps / seconds / 1e12
-    threads = host_threads()
+    threads = use_all_host_threads()
     sample = (f"{rows} of {m} rows of A against {cols} of {n} rows of B, all of K, per step: "
               f"dequantise/upcast + float32 (float64 for s8) matmul, numpy/BLAS")
     line = {
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": name, "data": "synthetic",
-        "config": {"workload": work["what"] + " (reference's CPU path on the host cores)"},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": name, "data": "synthetic",
+        "config": config_of(work, world),
+        "arm": "the reference's CPU path (its correctness oracle) on the host cores, numpy port",
         "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -300,22 +395,27 @@ def time_launches(torch, fn, steps):
 
 
 class Runner:
-    """Operand sets rotated past 2 x L2, the bound kernel, and one-step callables."""
+    """Operand sets rotated past 2 x L2, the bound kernel, and one-step callables.
+    Rank `rank` of `world` owns its rows of B (drawn from its own seed)."""
 
-    def __init__(self, torch, work, device, seed0, max_bytes=24 << 30):
+    def __init__(self, torch, work, device, seed0, world=1, rank=0, max_bytes=24 << 30):
         from opengemm_b200 import capi
         from opengemm_b200.configs import resolve_config
         from opengemm_b200.dtypes import DTYPES
+        from opengemm_b200.shard import shard_bounds
 
         self.torch = torch
-        name, m, n, k = work["name"], work["m"], work["n"], work["k"]
+        self.name, self.m, self.k = work["name"], work["m"], work["k"]
+        n0, n1 = shard_bounds(work["n"], world, rank)
+        self.n = n1 - n0
+        name, m, n, k = self.name, self.m, self.n, self.k
         self.d = DTYPES[name]
         self.per_set = algorithmic_bytes(name, m, n, k)
         self.copies = int(max(2, min(-(-2 * L2_BYTES // self.per_set), max_bytes // self.per_set)))
         self.sets = []
         for i in range(self.copies):
-            a, b, sfa, sfb = make_operands(torch, name, m, n, k, seed0 + i, device)
-            self.sets.append((a, b, sfa, sfb, torch.empty((m, n), device=device, dtype=self.d.out)))
+            ops = make_operands(torch, name, m, n, k, seed0 + i, device, seed_b=(seed0 + i) * 1000 + 7 + rank)
+            self.sets.append((ops, torch.empty((m, n), device=device, dtype=self.d.out)))
         self.lib, self.g = capi.bind(name, m, n, k, resolve_config(name, m, n, k))
         # Every operand set here is written once, before any timing, so no kernel of
         # the stream ever produces another's operands: say so, and operand loads of
@@ -325,9 +425,34 @@ class Runner:
         self.i = 0
 
     def step(self):
-        a, b, sfa, sfb, out = self.sets[self.i % self.copies]
+        ops, out = self.sets[self.i % self.copies]
         self.i += 1
-        self.lib.launch(self.g, a, b, sfa, sfb, out)
+        self.lib.launch(self.g, ops.a, ops.b, ops.sfa, ops.sfb, out)
+
+    def parity(self):
+        """The first operand set's output against the CPU oracle (sentinel-filled first)."""
+        ops, out = self.sets[0]
+        out.view(self.torch.uint8).fill_(0x7F)
+        self.lib.launch(self.g, ops.a, ops.b, ops.sfa, ops.sfb, out)
+        self.torch.cuda.synchronize()
+        return sampled_oracle_check(self.torch, self.name, self.k, ops, out)
+
+    def rate(self, us, unit):
+        return (self.per_set / us / 1e3) if unit == "GB/s" else (2.0 * self.m * self.n * self.k / us / 1e6)
+
+    def limiter(self):
+        """What bounds this shape's per-GPU rate, read off the tile plan."""
+        p = self.plan
+        slots = SM_COUNT // p["cta_group"]
+        waves = p["tiles"] / slots
+        if p["tiles"] < slots:
+            return f"SM coverage: {p['tiles'] * p['cta_group']} of {SM_COUNT} SMs hold a tile"
+        return (f"wave quantisation: {p['tiles']} tiles of {p['tile_m']}x{p['tile_n']} on {slots} "
+                f"{'pairs' if p['cta_group'] == 2 else 'CTAs'} = {waves:.2f} waves")
+
+
+def best_us(torch, fn, steps, repeats=3):
+    return min(time_launches(torch, fn, steps) for _ in range(repeats)) * 1e3 / steps
 
 
 def side_configs(torch, device, skip):
@@ -339,14 +464,25 @@ def side_configs(torch, device, skip):
         work = WORKLOADS[key]
         try:
             r = Runner(torch, work, device, seed0=50, max_bytes=8 << 30)
+            parity = r.parity()
             for _ in range(3):
                 r.step()
             torch.cuda.synchronize()
-            us = min(time_launches(torch, r.step, steps) for _ in range(3)) * 1e3 / steps
-            m, n, k = work["m"], work["n"], work["k"]
-            results[key] = {"dtype": work["name"], "mnk": [m, n, k], "us": round(us, 2),
-                            "tflops": round(2.0 * m * n * k / us / 1e6, 1),
-                            "gbs": round(r.per_set / us / 1e3, 1), "tile": r.plan}
+            us = best_us(torch, r.step, steps)
+            unit, _ = unit_of(work)
+            results[key] = {"dtype": work["name"], "mnk": [r.m, r.n, r.k], "us": round(us, 2),
+                            "tflops": round(2.0 * r.m * r.n * r.k / us / 1e6, 1),
+                            "gbs": round(r.per_set / us / 1e3, 1), "tile": r.plan, "parity_ok": parity["ok"],
+                            "parity_max_rel": parity["max_rel"]}
+            if key == "c5":
+                # Consecutive launches overlap (each starts loading while its predecessor
+                # drains); with the operands declared dependent again every launch waits
+                # for the previous one to finish: the single-launch figure.
+                r.lib.set_independent_inputs(False)
+                serial = best_us(torch, r.step, steps)
+                r.lib.set_independent_inputs(True)
+                results[key].update({"us_is": "consecutive launches overlapping", "us_serialised": round(serial, 2),
+                                     "gbs_serialised": round(r.per_set / serial / 1e3, 1)})
             del r
             torch.cuda.empty_cache()
         except Exception as exc:  # a side measurement must never cost the headline
@@ -367,7 +503,7 @@ def side_configs(torch, device, skip):
         for _ in range(3):
             quantize_step()
         torch.cuda.synchronize()
-        us = min(time_launches(torch, quantize_step, 10) for _ in range(3)) * 1e3 / 10
+        us = best_us(torch, quantize_step, 10)
         nbytes = rows * k * 2 + rows * k // 2 + rows * k // 16
         results["quantize_nvfp4_28672x8192"] = {"us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1),
                                                 "algorithmic_bytes": nbytes}
@@ -375,7 +511,7 @@ def side_configs(torch, device, skip):
         torch.cuda.empty_cache()
     except Exception as exc:
         results["quantize_nvfp4_28672x8192"] = {"error": str(exc)[:160]}
-    # The headline product with C rounded to bfloat16 on the way out (an output
+    # The fp8 product with C rounded to bfloat16 on the way out (an output
     # variant of this build; the reference writes float32 only).
     try:
         from opengemm_b200 import capi
@@ -391,13 +527,13 @@ def side_configs(torch, device, skip):
         def bf16_step():
             i = state["i"] % r.copies
             state["i"] += 1
-            a, b, _, _, _ = r.sets[i]
-            lib.launch(g, a, b, None, None, outs[i])
+            ops, _ = r.sets[i]
+            lib.launch(g, ops.a, ops.b, None, None, outs[i])
 
         for _ in range(3):
             bf16_step()
         torch.cuda.synchronize()
-        us = min(time_launches(torch, bf16_step, 50) for _ in range(3)) * 1e3 / 50
+        us = best_us(torch, bf16_step, 50)
         results["c2_bf16_output"] = {"dtype": name + ".bf16", "mnk": [m, n, k], "us": round(us, 2),
                                      "tflops": round(2.0 * m * n * k / us / 1e6, 1)}
         del r, outs
@@ -407,10 +543,64 @@ def side_configs(torch, device, skip):
     return results
 
 
+def sharded_configs(torch, dist, device, world, rank, skip, shard_counts):
+    """The N-sharded configurations, strong-scaled: for each, this rank's shard
+    of the `g`-way split timed on every rank at once (max over ranks), the
+    whole shape on one GPU beside it, and the per-GPU efficiency between them.
+    With one rank, `shard_counts` names the splits whose first shard to time."""
+    results = {}
+    for key in SHARDED:
+        if key == skip:
+            continue
+        work = WORKLOADS[key]
+        unit, _ = unit_of(work)
+        steps = {"c3": 10, "c4": 6, "c5": 50}[key]
+        try:
+            full = Runner(torch, work, device, seed0=90, max_bytes=4 << 30)
+            for _ in range(3):
+                full.step()
+            torch.cuda.synchronize()
+            full_us = best_us(torch, full.step, steps)
+            full_rate = full.rate(full_us, unit)
+            entry = {"dtype": work["name"], "mnk": [full.m, full.n, full.k], "unit": unit,
+                     "one_gpu": {"us": round(full_us, 2), "rate": round(full_rate, 1), "limiter": full.limiter()}}
+            del full
+            torch.cuda.empty_cache()
+            for g in shard_counts:
+                r = Runner(torch, work, device, seed0=90, world=g, rank=rank if world > 1 else 0, max_bytes=4 << 30)
+                parity = r.parity()
+                for _ in range(3):
+                    r.step()
+                torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                    torch.cuda.synchronize()
+                us = best_us(torch, r.step, max(steps, 20))
+                if world > 1:
+                    t = torch.tensor([us], device=device)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    us = float(t.item())
+                rate = r.rate(us, unit)
+                entry[f"shard_of_{g}"] = {
+                    "mnk": [r.m, r.n, r.k], "us": round(us, 2), "per_gpu_rate": round(rate, 1),
+                    "efficiency_vs_one_gpu": round(rate / full_rate, 3), "tile": r.plan, "limiter": r.limiter(),
+                    "parity_ok": parity["ok"], "timed_on": f"{world} GPU(s) at once" if world > 1 else "one GPU, first shard",
+                }
+                del r
+                torch.cuda.empty_cache()
+            results[key] = entry
+        except Exception as exc:
+            if world > 1:  # the other ranks are inside the same collectives: fail loudly, not silently apart
+                raise
+            results[key] = {"error": str(exc)[:200]}
+    return results
+
+
 def library_baseline(torch, r, steps):
     """cuBLAS / cuBLASLt on the first operand set, where torch exposes a kernel for the format."""
-    a, b, sfa, sfb, _ = r.sets[0]
-    name = r.work["name"]
+    ops, _ = r.sets[0]
+    a, b, sfa, sfb = ops.a, ops.b, ops.sfa, ops.sfb
+    name = r.name
     one = torch.ones((), device=a.device)
     if name == "bf16":
         f = lambda: torch.mm(a, b.t())
@@ -426,6 +616,71 @@ def library_baseline(torch, r, steps):
         f()
     torch.cuda.synchronize()
     return time_launches(torch, f, steps) * 1e3 / steps
+
+
+def reference_kernel_leg(torch, r, unit):
+    """The reference's own sm_100a kernel on the same operand rotation,
+    timed in windows alternating with this library's: a side measurement,
+    present only when the reference's libraries were built beside the oracle
+    (oracle/build_reference_kernels.py).  Never the `--impl reference` arm."""
+    from opengemm_b200 import compare
+
+    found = compare.reference_libraries(ROOT / "oracle" / "_ref")
+    if found is None:
+        return {"unavailable": "the reference's kernel libraries are not built under oracle/_ref"}
+    sets = [(ops.a, ops.b, ops.sfa, ops.sfb, out) for ops, out in r.sets]
+    result = compare.interleaved(found, r.name, r.m, r.n, r.k, sets, ours=(r.lib, r.g), windows=4, window_ms=60.0)
+    if "ref_us" in result:
+        result["ref_rate"] = round(r.rate(result["ref_us"], unit), 1)
+        result["ours_rate"] = round(r.rate(result["ours_us"], unit), 1)
+    return result
+
+
+def bind_memory_near(device_index):
+    """Prefer host memory on the NUMA node of GPU `device_index` for the pages
+    this process touches next (the pinned staging buffers), so each rank's
+    copies cross its own socket's PCIe root.  Returns a note for the JSON line
+    and a callable that puts the thread's CPU affinity and memory policy back."""
+    before = os.sched_getaffinity(0) if hasattr(os, "sched_getaffinity") else None
+    libc = ctypes.CDLL(None, use_errno=True)
+    SYS_set_mempolicy = 238  # x86-64
+
+    def restore():
+        try:
+            libc.syscall(SYS_set_mempolicy, 0, None, ctypes.c_ulong(0))  # MPOL_DEFAULT
+            if before is not None:
+                os.sched_setaffinity(0, before)
+        except Exception:
+            pass
+
+    return _bind_memory_near(device_index, libc, SYS_set_mempolicy), restore
+
+
+def _bind_memory_near(device_index, libc, SYS_set_mempolicy):
+    try:
+        import torch
+
+        props = torch.cuda.get_device_properties(device_index)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        node = int(Path(f"/sys/bus/pci/devices/{bus}/numa_node").read_text())
+        if node < 0:
+            return f"GPU {bus} reports no NUMA node"
+        mask = ctypes.c_ulong(1 << node)
+        MPOL_PREFERRED = 1
+        if libc.syscall(SYS_set_mempolicy, MPOL_PREFERRED, ctypes.byref(mask), ctypes.c_ulong(64)) != 0:
+            return f"set_mempolicy(node {node}) refused: errno {ctypes.get_errno()}"
+        cpus = Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip()
+        allowed = os.sched_getaffinity(0)
+        wanted = set()
+        for part in cpus.split(","):
+            lo, _, hi = part.partition("-")
+            wanted.update(range(int(lo), int(hi or lo) + 1))
+        if wanted & allowed:
+            os.sched_setaffinity(0, wanted & allowed)
+            return f"host pages preferred on NUMA node {node} (GPU {bus}); thread on its CPUs"
+        return f"host pages preferred on NUMA node {node} (GPU {bus}); its CPUs are outside this process's affinity"
+    except Exception as exc:
+        return f"not bound: {str(exc)[:80]}"
 
 
 def run_ours(args):
@@ -445,9 +700,9 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
 
     work = WORKLOADS[args.workload]
-    name, m, n, k = work["name"], work["m"], work["n"], work["k"]
-    r = Runner(torch, work, device, seed0=1000 * rank)
-    r.work = work
+    name, m, n_full, k = work["name"], work["m"], work["n"], work["k"]
+    r = Runner(torch, work, device, seed0=1000, world=world, rank=rank)
+    n = r.n
 
     def barrier():
         torch.cuda.synchronize()
@@ -461,6 +716,17 @@ def run_ours(args):
         t = torch.tensor([x], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    # Parity gate: untimed, before the warm-up; every rank checks its own shard.
+    parity = r.parity()
+    all_ok = max_over_ranks(0.0 if parity["ok"] else 1.0) == 0.0
+    if not all_ok:
+        if not parity["ok"]:
+            print(json.dumps({"parity": parity, "rank": rank, "error": "output outside tolerance; nothing timed"}),
+                  file=sys.stderr, flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        raise SystemExit(3)
 
     warmup = max(args.warmup, 3)
     for _ in range(warmup):
@@ -476,30 +742,34 @@ def run_ours(args):
     barrier()
     ms = max_over_ranks(ms)
     t_end = time.time()
-    if rank == 0 and t_end - t_begin < 0.6:
+    if rank == 0 and t_end - t_begin < 0.6 and world == 1:
         # the same load a little longer, so the 100 ms clock sampler sees it
         while time.time() - t_begin < 0.6:
             time_launches(torch, r.step, max(args.steps // 4, 1))
         t_end = time.time()
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
 
-    flops_step = 2.0 * m * n * k
     unit, metric = unit_of(work)
     kernel_us = ms * 1e3 / args.steps
-    per_gpu = (r.per_set / kernel_us / 1e3) if unit == "GB/s" else (flops_step / kernel_us / 1e6)
-    value = per_gpu * world
+    flops_job = 2.0 * m * n_full * k
+    bytes_job = algorithmic_bytes(name, m, n_full, k)
+    per_gpu = r.rate(kernel_us, unit)                      # this shard's work over the slowest rank's time
+    value = (bytes_job / kernel_us / 1e3) if unit == "GB/s" else (flops_job / kernel_us / 1e6)
 
     # End to end through the public API, every step fed from pinned host memory:
-    # host->device copies of the step's operands, gemm(), device->host copy of
-    # the result.  Three streams and two sets of buffers let step i+1's upload
-    # run under step i's download (the link is full duplex); every step still
-    # performs all three, in order, on its own buffers.
-    a0, b0, sfa0, sfb0, _ = r.sets[0]
-    host_in = [t.cpu().pin_memory() for t in (a0, b0, sfa0, sfb0) if t is not None]
+    # host->device copies of the step's operands (A and its scales whole, this
+    # rank's rows of B and of B's scales), gemm(), device->host copy of this
+    # rank's columns of C.  Three streams and two sets of buffers let step i+1's
+    # upload run under step i's download (the link is full duplex); every step
+    # still performs all three, in order, on its own buffers.
+    numa_note, restore_host_binding = bind_memory_near(local)
+    ops0, _ = r.sets[0]
+    dev_tensors = [t for t in (ops0.a, ops0.b, ops0.sfa, ops0.sfb) if t is not None]
+    host_in = [t.cpu().pin_memory() for t in dev_tensors]
     lanes = []
     for _ in range(2):
         lanes.append({
-            "dev_in": [torch.empty_like(t) for t in (a0, b0, sfa0, sfb0) if t is not None],
+            "dev_in": [torch.empty_like(t) for t in dev_tensors],
             "dev_c": torch.empty((m, n), device=device, dtype=r.d.out),
             "host_c": torch.empty((m, n), dtype=r.d.out).pin_memory(),
             "uploaded": torch.cuda.Event(), "computed": torch.cuda.Event(), "downloaded": torch.cuda.Event(),
@@ -547,9 +817,17 @@ def run_ours(args):
     barrier()
     e2e_ms = max_over_ranks(e2e_ms)
     e2e_us = e2e_ms * 1e3 / e2e_steps
-    e2e_value = world * ((r.per_set / e2e_us / 1e3) if unit == "GB/s" else (flops_step / e2e_us / 1e6))
+    e2e_value = (bytes_job / e2e_us / 1e3) if unit == "GB/s" else (flops_job / e2e_us / 1e6)
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = lanes[0]["host_c"].numel() * lanes[0]["host_c"].element_size()
+    # the end-to-end output is the product too: same check on this rank's last lane
+    e2e_parity = sampled_oracle_check(torch, name, k, ops0, torch.as_tensor(lanes[(state["i"] - 1) % 2]["host_c"]).to(device))
+    del lanes, host_in
+    torch.cuda.empty_cache()
+    restore_host_binding()
+
+    shard_counts = [world] if world > 1 else [2, 4, 8]
+    sharded = None if args.no_side else sharded_configs(torch, dist, device, world, rank, None, shard_counts)
 
     if rank != 0:
         if world > 1:
@@ -557,9 +835,10 @@ def run_ours(args):
         return
 
     peaks = measured_peaks()
+    traffic = NCU_TRAFFIC_BYTES.get((name, m, n, k))
     if unit == "GB/s":
         roofline = {"bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": per_gpu / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                    "frac": per_gpu / peaks["hbm_gbs"], "traffic": traffic,
                     "peak_source": f"{peaks['source']} copy bandwidth", "algorithmic_bytes_per_launch": r.per_set}
     else:
         rate = RATE_VS_BF16[name]
@@ -568,46 +847,53 @@ def run_ours(args):
         peak = rate * base
         how = "" if rate == 1.0 else f"{rate:g} x "
         roofline = {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak,
-                    "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                    "traffic": traffic,
                     "peak_source": f"{how}{peaks['source']} bf16 {'burst' if burst else 'sustained'} ({base} TFLOP/s)"
                                    + ("" if rate == 1.0 else "; this format's own peak is not measured on the pool"),
                     "frac_of_nominal": per_gpu / (rate * NOMINAL_BF16_TFLOPS),
-                    "algorithmic_flops_per_launch": flops_step}
+                    "algorithmic_flops_per_launch": 2.0 * m * n * k,
+                    "per": "GPU: this rank's shard over the slowest rank's time per launch"}
     try:
         lib_us = library_baseline(torch, r, args.steps)
-        roofline["cublas_same_shape"] = None if lib_us is None else (
-            r.per_set / lib_us / 1e3 if unit == "GB/s" else flops_step / lib_us / 1e6)
+        roofline["cublas_same_shape"] = None if lib_us is None else r.rate(lib_us, unit)
     except Exception as exc:
         roofline["cublas_same_shape"] = None
         roofline["cublas_note"] = str(exc)[:100]
+    try:
+        roofline["reference_kernel_same_shape"] = reference_kernel_leg(torch, r, unit)
+    except Exception as exc:
+        roofline["reference_kernel_same_shape"] = {"unavailable": str(exc)[:160]}
 
     cpu = None
     if world == 1:
         seconds, rows, cols, _ = cpu_sample(name, m, n, k, budget_s=10.0)
         cpu_value = (algorithmic_bytes_np(name, rows, cols, k) / seconds / 1e9) if unit == "GB/s" else (
             2.0 * rows * cols * k / seconds / 1e12)
-        cpu = {"value": cpu_value, "unit": unit, "cores": host_threads(), "kind": "port",
+        cpu = {"value": cpu_value, "unit": unit, "cores": use_all_host_threads(), "kind": "port",
                "sample": f"{rows} of {m} rows of A against {cols} of {n} rows of B, all of K, once ({seconds:.2f} s): "
                          f"dequantise/upcast + float32 (float64 for s8) matmul, numpy/BLAS"}
     others = side_configs(torch, device, args.workload) if (world == 1 and not args.no_side) else None
 
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-        "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": name, "data": "synthetic",
-        "config": {
-            "workload": work["what"] + f"; per GPU (N-sharded: global N = {n} x GPUs)",
-            "m": m, "n_per_gpu": n, "k": k,
-            "l2": f"rotating {r.copies} operand/output sets ({r.copies * r.per_set >> 20} MiB > 2 x L2)",
-            "tile": r.plan, "parallelism": f"nshard{world}",
+        "config": config_of(work, world),
+        "kernel": {
+            "shard_mnk": [m, n, k], "tile": r.plan, "limiter": r.limiter(),
+            "rotation": f"{r.copies} operand/output sets ({r.copies * r.per_set >> 20} MiB > 2 x L2)",
             "launch": "programmatic dependent launch; operands declared independent of earlier kernels "
                       "(og_b200_set_independent_inputs), output stores wait for the previous grid",
         },
+        "parity": parity,
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
+                "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps, "parity_ok": e2e_parity["ok"],
+                "bytes_are": "per rank", "host_memory": numa_note},
         "gpu_launches": args.steps * world, "clocks": clocks,
     }
+    if sharded is not None:
+        line["sharded_configs"] = sharded
     if others is not None:
         line["other_configs"] = others
     print(json.dumps(line), flush=True)
@@ -618,11 +904,11 @@ def run_ours(args):
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
-    parser.add_argument("--warmup", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=100)
+    parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    parser.add_argument("--workload", choices=sorted(WORKLOADS), default="c2",
-                        help="which baseline configuration to run (default: the fp8 headline)")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS), default=HEADLINE,
+                        help="which baseline configuration to run (default: c4, the largest single-GPU one)")
     parser.add_argument("--no-side", action="store_true", help="skip the brief measurements of the other configurations")
     args = parser.parse_args()
     if args.impl == "reference":

@@ -13,8 +13,9 @@
  * owned by the caller; the library keeps no reference to them after a call
  * returns.  It allocates no device memory, with one exception: the first launch
  * on a device that asks for the stream-K schedule (split_k >= 2) allocates
- * that schedule's scratch (about 76 MB) for the life of the process.  Launches
- * are asynchronous on the stream given.
+ * that schedule's scratch (about 76 MB) for the life of the process, unless
+ * og_b200_prepare_device did so earlier.  Launches are asynchronous on the
+ * stream given.  Devices 0..63 are served.
  */
 #ifndef OPENGEMM_B200_H
 #define OPENGEMM_B200_H
@@ -41,7 +42,7 @@ enum {
   OG_ERR_NO_KERNEL = -2, /* no kernel can serve the configuration */
   OG_ERR_TENSORMAP = -3,
   OG_ERR_LAUNCH = -4,
-  OG_ERR_TIMEOUT = -5    /* a device-side wait ran out (og_b200_status) */
+  OG_ERR_TIMEOUT = -5    /* a device-side wait ran out: what og_b200_status answers for a non-zero status word */
 };
 
 /* One GEMM: shape, the configs.json entry that picks and drives the kernel,
@@ -98,8 +99,15 @@ OG_API int32_t og_smm_launch(const OgGemm* g, const void* a, const void* b, cons
  * "<format>.bf16" for every dense float format ("bf16.bf16", "f16.bf16", "tf32.bf16",
  * "e4m3.bf16", "e5m2.bf16", "e3m2.bf16", "e2m3.bf16", "e2m1.bf16", "e4m3xe5m2.bf16"):
  * same operands and tile plans, the f32 accumulator rounded to bfloat16 (nearest
- * even) on the way out, C a row-major bfloat16 [m, n].  og_mm_kernels / og_mm_kernel
- * enumerate the reference's formats only. */
+ * even) on the way out, C a row-major bfloat16 [m, n]; and "<format>.f16" for the
+ * same nine, C a row-major IEEE half [m, n].  og_mm_kernels / og_mm_kernel
+ * enumerate the reference's formats only.
+ *
+ * Rasterisation: OgGemm.walk selects the order tiles are visited in, with the
+ * reference's numbering (opengemm/src/mm/types.cuh:78-84): 0 bands `supergroup`
+ * tiles wide along N; 1 the same, serpentine; 2 blocks inside a band; 3 a
+ * generalised Hilbert curve; 4 bands along M.  Block-scaled formats, whose
+ * reference struct carries no walk, use 0. */
 
 /* The native tile plan of a bound GEMM, for tuners and reports. */
 typedef struct {
@@ -122,10 +130,16 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out);
 
 /* Launch like og_mm_launch / og_smm_launch (chosen by g->dtype) with a device status
  * word: `status` points to a zero-initialised int32 in device-accessible memory.  A wait
- * that gives up stores (site | cta << 8) there instead of spinning forever. */
+ * that gives up stores (site | cta << 8) there instead of spinning forever; the kernel
+ * then leaves through its ordinary teardown and the context stays usable.  Read the word
+ * back after synchronising and hand it to og_b200_status. */
 OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void* b,
                                       const void* sfa, const void* sfb, void* c, int32_t device,
                                       void* stream, int32_t* status);
+
+/* Turns the status word of og_b200_launch_checked into a return code: OG_OK for 0,
+ * else OG_ERR_TIMEOUT with og_mm_error() naming the wait (which role, which CTA). */
+OG_API int32_t og_b200_status(int32_t status_word);
 
 /* Launch like og_mm_launch / og_smm_launch (chosen by g->dtype) with every output
  * multiplied by `alpha` in float32 before it is stored (the product of per-tensor
@@ -134,6 +148,30 @@ OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void
 OG_API int32_t og_b200_launch_alpha(const OgGemm* g, const void* a, const void* b,
                                     const void* sfa, const void* sfb, void* c, int32_t device,
                                     void* stream, float alpha);
+
+/* Output variant: C = alpha * (A . B^T) + bias, with `bias` a float32 device vector of
+ * n values, one per column of C, added in float32 before the store (alpha = 1 adds the
+ * bias only).  Float formats only.  The reference's epilogues store the bare product
+ * (opengemm/src/mm/kernel.cuh:410-596, opengemm/src/smm/kernel.cuh:374-598). */
+OG_API int32_t og_b200_launch_bias(const OgGemm* g, const void* a, const void* b,
+                                   const void* sfa, const void* sfb, void* c, int32_t device,
+                                   void* stream, float alpha, const void* bias);
+
+/* Do now what launches on `device` do on first use: opt every kernel into its shared
+ * memory and allocate the stream-K workspaces.  Call it before capturing launches into
+ * a CUDA graph, or to keep the first request of a server free of allocations. */
+OG_API int32_t og_b200_prepare_device(int32_t device);
+
+/* The order a bound `g` visits its output tiles in: writes (M index, N index) pairs for
+ * tile 0, 1, ... into `out` (room for `cap` integers) and returns the number of tiles,
+ * or a negative status.  Needs no GPU. */
+OG_API int32_t og_b200_tile_order(const OgGemm* g, int32_t* out, int32_t cap);
+
+/* Testing aid.  The calling thread's next launch credits `bytes` more to each of its
+ * stage barriers than its loads deliver, so the first wait for data runs out after the
+ * limit of og_b200_set_wait_limit_ms and the launch reports it through its status word.
+ * Nothing faults and nothing spins without bound. */
+OG_API void og_b200_test_overcredit_next_launch(int32_t bytes);
 
 /* The complete tile plan of a bound `g` for a device of `sm_count` SMs, as one JSON
  * object of integers written to `out` (what the standalone-kernel emitter bakes
@@ -163,7 +201,8 @@ OG_API const char* og_b200_quantize_error(void);
  * (opengemm/src/mm/kernel.cuh:209,479-483).  Default 0. */
 OG_API void og_b200_set_independent_inputs(int32_t yes);
 
-/* Limit of every device-side wait in milliseconds (default 2000). */
+/* Limit of every device-side wait in milliseconds (default 2000).  Waits for a whole
+ * accumulator, which sit behind a K loop of the others, allow twice as long. */
 OG_API void og_b200_set_wait_limit_ms(int32_t ms);
 
 /* No counterpart in the reference.  The same launch as og_mm_launch / og_smm_launch

@@ -12,7 +12,7 @@ import torch
 
 from . import capi
 from .configs import resolve_config
-from .dtypes import BF16_OUT, BF16_OUT_SUFFIX, DTYPES, base_name, dtype_name, extent, k_of, lookup, sf_block
+from .dtypes import DTYPES, NARROW_OUT, NARROW_OUT_SUFFIXES, base_name, dtype_name, extent, k_of, lookup, sf_block
 
 _bound = {}  # (dtype name, m, n, k) -> (Library, OgGemm), for the life of the process
 
@@ -27,7 +27,7 @@ def bind(name, m, n, k, device):
 
 def forget(name=None):
     """Drop memoised bindings (after the stored configurations changed)."""
-    for key in [key for key in _bound if name is None or key[0] == name]:
+    for key in [key for key in _bound if name is None or base_name(key[0]) == name]:
         del _bound[key]
 
 
@@ -75,7 +75,7 @@ def output(d, m, n, out, device):
     return out
 
 
-def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=None, alpha=None):
+def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=None, alpha=None, bias=None):
     """Compute C[M, N] = A[M, K] @ B[N, K].T.
 
     Args:
@@ -87,35 +87,46 @@ def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=N
         out: output to write into instead of allocating one.
         atype: element name for a `uint8` operand: "u8", "e3m2", "e2m3" or "e2m1".
         btype: element name for `b`; defaults to `atype` when the dtypes match.
-        out_dtype: `torch.bfloat16` makes a dense float format round its f32
-            accumulator to bfloat16 on the way out (an addition of this build;
-            the default, None, is the reference's output type).  Implied by a
-            bfloat16 `out`.
+        out_dtype: `torch.bfloat16` or `torch.float16` makes a dense float
+            format round its f32 accumulator to that type on the way out (an
+            addition of this build; the default, None, is the reference's
+            output type).  Implied by an `out` of that dtype.
         alpha: a Python float every output is multiplied by (in float32) before
             it is stored, e.g. the product of per-tensor scales of fp8 operands
             (an addition of this build; float formats only).
+        bias: a float32 CUDA vector of N values added to every row of C (after
+            `alpha`, in float32, before the store; an addition of this build;
+            float formats only).
 
     Returns:
         `(M, N)` row-major: float32 for dense formats (bfloat16 with
-        `out_dtype=torch.bfloat16`), int32 for s8 and u8, bfloat16 for
-        block-scaled ones.
+        `out_dtype=torch.bfloat16`, float16 with `out_dtype=torch.float16`), int32
+        for s8 and u8, bfloat16 for block-scaled ones.
     """
     name = dtype_name(a, b, sfa, atype, btype)
-    if out_dtype is None and out is not None and out.dtype is torch.bfloat16 and DTYPES[name].out is torch.float32:
-        out_dtype = torch.bfloat16
+    if out_dtype is None and out is not None and out.dtype in NARROW_OUT_SUFFIXES and DTYPES[name].out is torch.float32:
+        out_dtype = out.dtype
     if out_dtype is not None and out_dtype is not DTYPES[name].out:
-        if out_dtype is not torch.bfloat16 or name + BF16_OUT_SUFFIX not in BF16_OUT:
-            raise TypeError(f"{name} writes {DTYPES[name].out}; only dense float formats can write torch.bfloat16 instead")
-        name += BF16_OUT_SUFFIX
+        suffix = NARROW_OUT_SUFFIXES.get(out_dtype)
+        if suffix is None or name + suffix not in NARROW_OUT:
+            raise TypeError(f"{name} writes {DTYPES[name].out}; only dense float formats can write "
+                            f"torch.bfloat16 or torch.float16 instead")
+        name += suffix
     d = lookup(name)
     m, n, k = a.size(0), b.size(0), k_of(d, a.size(1))
     check_operands(d, m, n, k, a, b, sfa, sfb)
     lib, g = _bound.get((name, m, n, k)) or bind(name, m, n, k, a.device)
     out = output(d, m, n, out, a.device)
-    if alpha is None:
+    if alpha is None and bias is None:
         lib.launch(g, a, b, sfa, sfb, out)
-    else:
-        if d.out is torch.int32:
-            raise TypeError(f"{name} accumulates integers exactly: its output cannot be scaled")
+        return out
+    if d.out is torch.int32:
+        raise TypeError(f"{name} accumulates integers exactly: its output cannot be scaled or biased")
+    if bias is None:
         lib.launch_alpha(g, a, b, sfa, sfb, out, alpha)
+        return out
+    if not (bias.is_cuda and bias.device == a.device and bias.dtype is torch.float32 and bias.is_contiguous()
+            and bias.shape == (n,)):
+        raise TypeError(f"bias must be a contiguous float32 [{n}] on {a.device}")
+    lib.launch_bias(g, a, b, sfa, sfb, out, 1.0 if alpha is None else alpha, bias)
     return out

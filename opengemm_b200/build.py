@@ -1,12 +1,25 @@
-"""Build libopengemm_b200.so in-tree with nvcc, for sm_100a only.
+"""Build libopengemm_b200.so with nvcc, for sm_100a only.
 
-The reference JIT-compiles two libraries into a content-hashed cache
-(opengemm/python/build.py:98-125); here one library serves both, sits beside
-the package in `opengemm_b200/lib/`, and is rebuilt when any source is newer
-than it.  `OPENGEMM_LIB_MM` / `OPENGEMM_LIB_SMM` still override the path, as
-in the reference (build.py:100-102).
+Where the library comes from follows the reference's rules
+(opengemm/python/build.py:21-24,70-125) with one library serving both
+implementations:
+
+* `OPENGEMM_LIB_MM` / `OPENGEMM_LIB_SMM` name a library to load as is.
+* Otherwise the in-tree build, `opengemm_b200/lib/libopengemm_b200.so`, is
+  used while the digest recorded beside it (`lib/stamp.json`) still matches
+  the sources' content - content, not modification times, which a checkout
+  or an installer rewrites.  A stale or missing in-tree library is rebuilt in
+  place.
+* `OPENGEMM_JIT=1` sets the in-tree library aside: the library is compiled
+  into a cache directory (`OPENGEMM_CACHE`, else `$XDG_CACHE_HOME/opengemm_b200`,
+  else `~/.cache/opengemm_b200`) under a key that digests the sources, the
+  compiler's version and the flags, and is reused from there.  The same cache
+  takes over when the package directory cannot be written.
 """
 
+import functools
+import hashlib
+import json
 import os
 import subprocess
 import sys
@@ -45,20 +58,61 @@ def library_file():
     return LIB_DIR / LIB_NAME
 
 
+def source_hash():
+    """A digest of every source the library is built from: names and content."""
+    digest = hashlib.blake2s(digest_size=8)
+    units, headers = sources()
+    for path in sorted(units + headers):
+        digest.update(path.name.encode())
+        digest.update(path.read_bytes())
+    return digest.hexdigest()
+
+
+@functools.lru_cache(maxsize=None)
+def nvcc_version():
+    """The compiler's release line, or None when there is no nvcc to ask."""
+    try:
+        out = subprocess.run([nvcc_path(), "--version"], capture_output=True, text=True, check=True).stdout
+    except (OSError, subprocess.CalledProcessError):
+        return None
+    return next((line.strip() for line in out.splitlines() if "release" in line), "unknown")
+
+
+def build_hash():
+    """The cache key: the sources, the compiler and the flags that turn them into a library."""
+    digest = hashlib.blake2s(digest_size=8)
+    digest.update(source_hash().encode())
+    digest.update((nvcc_version() or "no nvcc").encode())
+    digest.update(" ".join(NVCC_FLAGS).encode())
+    return digest.hexdigest()
+
+
+def cache_dir():
+    root = os.environ.get("OPENGEMM_CACHE")
+    if root:
+        return Path(root)
+    return Path(os.environ.get("XDG_CACHE_HOME", Path.home() / ".cache")) / "opengemm_b200"
+
+
 def stale():
+    """True when the in-tree library is missing or was built from other sources."""
     lib = library_file()
     if not lib.exists():
         return True
-    units, headers = sources()
-    built = lib.stat().st_mtime
-    return any(p.stat().st_mtime > built for p in units + headers)
+    try:
+        stamp = json.loads((LIB_DIR / "stamp.json").read_text())
+    except (OSError, ValueError):
+        return True
+    return stamp.get("sources") != source_hash()
 
 
-def compile_library(verbose=False):
-    """Compile every translation unit (in parallel) and link the shared library."""
+def compile_library(verbose=False, out=None):
+    """Compile every translation unit (in parallel) and link the shared library
+    (`out`, default the in-tree file, whose stamp is written beside it)."""
     units, _ = sources()
-    LIB_DIR.mkdir(parents=True, exist_ok=True)
-    obj_dir = LIB_DIR / "obj"
+    target = Path(out) if out is not None else library_file()
+    target.parent.mkdir(parents=True, exist_ok=True)
+    obj_dir = target.parent / "obj"
     obj_dir.mkdir(exist_ok=True)
     nvcc = nvcc_path()
 
@@ -74,15 +128,26 @@ def compile_library(verbose=False):
     log(f"compiling {LIB_NAME} for sm_100a ({len(units)} translation units)")
     with ThreadPoolExecutor(max_workers=len(units)) as pool:
         objects = list(pool.map(one, units))
-    temporary = LIB_DIR / (LIB_NAME + ".tmp")
+    temporary = target.parent / f"{LIB_NAME}.{os.getpid()}.tmp"
     link = [nvcc, *ARCH, "-shared", "-Xcompiler", "-fPIC", *map(str, objects), "-o", str(temporary)]
     done = subprocess.run(link, capture_output=True, text=True)
     if done.returncode != 0:
+        temporary.unlink(missing_ok=True)
         raise RuntimeError("link failed:\n" + (done.stderr or done.stdout))
-    temporary.replace(library_file())
+    temporary.replace(target)
+    (target.parent / "stamp.json").write_text(json.dumps({"sources": source_hash(), "nvcc": nvcc_version(), "arch": ARCH[1]}))
     if verbose:
-        log(f"built {library_file()}")
-    return library_file()
+        log(f"built {target}")
+    return target
+
+
+def cached_library():
+    """The library under the cache directory for this exact build, compiled on first use."""
+    out = cache_dir() / build_hash() / LIB_NAME
+    if not out.exists():
+        log(f"compiles once, then cached at {out.parent}")
+        compile_library(out=out)
+    return out
 
 
 def library_path(impl):
@@ -92,9 +157,13 @@ def library_path(impl):
     override = os.environ.get(f"OPENGEMM_LIB_{impl.upper()}")
     if override:
         return Path(override)
+    if os.environ.get("OPENGEMM_JIT"):
+        return cached_library()
     if stale():
         try:
             compile_library()
+        except PermissionError:
+            return cached_library()
         except (OSError, RuntimeError) as exc:
             if not library_file().exists():
                 raise RuntimeError(

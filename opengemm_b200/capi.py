@@ -66,7 +66,9 @@ KERNEL_KEYS = {
 }
 LAUNCH_KEYS = {
     "mm": ("supergroup", "walk", "l2_promo"),
-    "smm": ("supergroup", "epi_direct", "persistent", "split_k"),  # split_k: an addition of this build
+    # split_k, walk, stages and l2_promo are additions of this build for the block-scaled formats
+    # (the struct has the fields; the reference's block-scaled library does not read them)
+    "smm": ("supergroup", "epi_direct", "persistent", "split_k", "walk", "stages", "l2_promo"),
 }
 # Defaults for keys an entry may omit (entries written by this build's tuner carry all of them).
 KEY_DEFAULTS = {
@@ -95,9 +97,11 @@ def scale_bytes(d, rows, k):
 class Library:
     """The shared library seen through one implementation's six entry points."""
 
-    def __init__(self, impl):
+    def __init__(self, impl, path=None):
+        """`path` loads another shared library that exports the same entry
+        points (a measuring tool's use); by default the in-tree build."""
         self.impl = impl
-        self.path = build.library_path(impl)
+        self.path = path if path is not None else build.library_path(impl)
         try:
             lib = ctypes.CDLL(str(self.path))
         except OSError as exc:
@@ -147,6 +151,17 @@ class Library:
             self._describe = lib.og_b200_describe
             self._describe.restype = c_int32
             self._describe.argtypes = [POINTER(OgGemm), c_int32, c_char_p, c_int32]
+            self._bias = lib.og_b200_launch_bias
+            self._bias.restype = c_int32
+            self._bias.argtypes = [POINTER(OgGemm)] + [c_void_p] * 5 + [c_int32, c_void_p, ctypes.c_float, c_void_p]
+            self._status = lib.og_b200_status
+            self._status.restype, self._status.argtypes = c_int32, [c_int32]
+            self._prepare = lib.og_b200_prepare_device
+            self._prepare.restype, self._prepare.argtypes = c_int32, [c_int32]
+            self._tile_order = lib.og_b200_tile_order
+            self._tile_order.restype, self._tile_order.argtypes = c_int32, [POINTER(OgGemm), POINTER(c_int32), c_int32]
+            self._overcredit = lib.og_b200_test_overcredit_next_launch
+            self._overcredit.restype, self._overcredit.argtypes = None, [c_int32]
         self._kernels = None
 
     def error(self):
@@ -218,6 +233,43 @@ class Library:
         )
         if status != OG_OK:
             raise RuntimeError(self.error())
+
+    def launch_bias(self, g, a, b, sfa, sfb, out, alpha, bias):
+        """Like `launch`, every output multiplied by `alpha` and the float32 vector `bias`
+        (one value per column of C) added, in float32, before it is stored."""
+        device = a.get_device()
+        status = self._bias(
+            byref(g), a.data_ptr(), b.data_ptr(),
+            0 if sfa is None else sfa.data_ptr(), 0 if sfb is None else sfb.data_ptr(),
+            out.data_ptr(), device, raw_stream(device), float(alpha), bias.data_ptr(),
+        )
+        if status != OG_OK:
+            raise RuntimeError(self.error())
+
+    def status(self, word):
+        """OG_OK for a zero status word of `launch_checked`, else OG_ERR_TIMEOUT with
+        `error()` naming the wait that gave up."""
+        return self._status(int(word))
+
+    def prepare_device(self, device):
+        """Do now what launches on `device` would do on first use (shared-memory
+        opt-in of every kernel, the stream-K workspaces), e.g. before a stream capture."""
+        if self._prepare(device) != OG_OK:
+            raise RuntimeError(self.error())
+
+    def tile_order(self, g):
+        """The (M index, N index) of every output tile of a bound GEMM, in the order the grid visits them."""
+        tiles = self.plan(g)["tiles"]
+        buffer = (c_int32 * (2 * tiles))()
+        count = self._tile_order(byref(g), buffer, 2 * tiles)
+        if count < 0:
+            raise RuntimeError(self.error())
+        return [(buffer[2 * i], buffer[2 * i + 1]) for i in range(count)]
+
+    def test_overcredit_next_launch(self, nbytes):
+        """Testing aid: the calling thread's next launch credits `nbytes` more to every
+        stage barrier than its loads deliver, so its first wait for data runs out."""
+        self._overcredit(int(nbytes))
 
     def plan(self, g, device=-1):
         out = OgPlan()

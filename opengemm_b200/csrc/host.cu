@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include "kernel.cuh"
+#include "launch_common.h"
 #include "plan.h"
 
 namespace og {
@@ -46,6 +47,9 @@ namespace {
 thread_local char error_text[320];
 std::atomic<long long> wait_limit_ns{2000ll * 1000 * 1000};
 std::atomic<int> independent_inputs{0};
+// Testing aid (og_b200_test_overcredit_next_launch): bytes added to what the
+// next launch on this thread credits to every stage barrier.
+thread_local int overcredit_next = 0;
 
 int fail(int code, const char* format, ...) {
   va_list args;
@@ -55,110 +59,31 @@ int fail(int code, const char* format, ...) {
   return code;
 }
 
-// cuTensorMapEncodeTiled, resolved through the runtime so that the library
-// loads (and bind / plan work) on a machine without a driver.
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                              CUtensorMapFloatOOBfill);
-
-EncodeFn encoder() {
-  static EncodeFn fn = [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) !=
-            cudaSuccess ||
-        result != cudaDriverEntryPointSuccess)
-      return EncodeFn(nullptr);
-    return reinterpret_cast<EncodeFn>(sym);
-  }();
-  return fn;
-}
-
-struct MapKey {
-  const void* base;
-  uint64_t dim0, dim1, stride;
-  uint32_t box0, box1;
-  int type, swizzle, l2;
-  bool operator==(const MapKey& o) const {
-    return base == o.base && dim0 == o.dim0 && dim1 == o.dim1 && stride == o.stride &&
-           box0 == o.box0 && box1 == o.box1 && type == o.type && swizzle == o.swizzle && l2 == o.l2;
-  }
-};
-
-struct MapSlot {
-  MapKey key{};
-  CUtensorMap map;
-  bool used = false;
-};
-
-constexpr int MAP_SLOTS = 256;
-thread_local MapSlot map_cache[MAP_SLOTS];
-
-uint64_t mix(uint64_t h, uint64_t v) {
-  h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
-  return h;
-}
-
-// A 2-D tiled map over `base`: dim0 innermost (elements), rows `stride` bytes
-// apart.  Out-of-bounds parts of a box read as zero and are clipped on store.
-int encode_2d(CUtensorMap* out, const void* base, int type, uint64_t dim0, uint64_t dim1,
-              uint64_t stride, uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle, int l2,
-              const char* which) {
-  const MapKey key{base, dim0, dim1, stride, box0, box1, type, int(swizzle), l2};
-  uint64_t h = mix(0, reinterpret_cast<uint64_t>(base));
-  h = mix(h, dim0 * 1315423911ull + dim1);
-  h = mix(h, (uint64_t(box0) << 32) | box1);
-  h = mix(h, stride * 31 + uint64_t(type) * 7 + uint64_t(swizzle) * 3 + uint64_t(l2));
-  MapSlot& slot = map_cache[h % MAP_SLOTS];
-  if (slot.used && slot.key == key) {
-    *out = slot.map;
-    return OG_OK;
-  }
-  EncodeFn encode = encoder();
-  if (!encode) return fail(OG_ERR_TENSORMAP, "cuTensorMapEncodeTiled is not available: no CUDA driver");
-  const cuuint64_t dims[2] = {dim0, dim1};
-  const cuuint64_t strides[1] = {stride};
-  const cuuint32_t box[2] = {box0, box1};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  const CUtensorMapL2promotion promo = l2 == 2   ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
-                                       : l2 == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
-                                                 : CU_TENSOR_MAP_L2_PROMOTION_NONE;
-  const CUresult status =
-      encode(out, CUtensorMapDataType(type), 2, const_cast<void*>(base), dims, strides, box,
-             elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (status != CUDA_SUCCESS)
-    return fail(OG_ERR_TENSORMAP,
-                "cuTensorMapEncodeTiled failed for %s (driver error %d; dims %llu x %llu, stride %llu, "
-                "box %u x %u, type %d)",
-                which, int(status), (unsigned long long)dim0, (unsigned long long)dim1,
-                (unsigned long long)stride, box0, box1, type);
-  slot.key = key;
-  slot.map = *out;
-  slot.used = true;
-  return OG_OK;
-}
-
 // Stream-K scratch: partial sums of tiles shared by two clusters, and the
 // flags that publish them.  One region per epilogue warp of a full grid;
-// WORKSPACES of them are used round-robin by successive launches so that a
-// launch never reuses the buffers of one that may still be running (each
-// launch fills the GPU, so no more than two or three can overlap).
+// WORKSPACES of them per device are used round-robin by that device's
+// successive stream-K launches.  A launch that takes a slot first makes its
+// stream wait for the slot's previous user (an event recorded behind that
+// launch), so launches on any number of streams never share a workspace while
+// either is running; with one stream the wait is already satisfied.
 constexpr int WORKSPACES = 4;
 constexpr size_t REGION_BYTES = 32 * 256 * 4;
+constexpr int MAX_DEVICES = 64;
 
 struct DeviceInfo {
   int sm_count = 0;
   uint64_t configured = 0;  // bit per kernel variant
+  unsigned epoch = 0;       // this device's stream-K launches so far
   float* partial[WORKSPACES] = {};
   int* flags[WORKSPACES] = {};
+  cudaEvent_t released[WORKSPACES] = {};  // recorded behind the slot's last user
 };
-std::atomic<unsigned> launch_epoch{0};
 std::mutex device_mutex;
-DeviceInfo devices[64];
+DeviceInfo devices[MAX_DEVICES];
 
 int follow_device(int device) {
+  if (device < 0 || device >= MAX_DEVICES)
+    return fail(OG_ERR_LAUNCH, "device %d is out of range: this library serves devices 0..%d", device, MAX_DEVICES - 1);
   int current = -1;
   if (cudaGetDevice(&current) != cudaSuccess) return fail(OG_ERR_LAUNCH, "cudaGetDevice failed");
   if (current != device) {
@@ -168,64 +93,94 @@ int follow_device(int device) {
   return OG_OK;
 }
 
-std::atomic<int> sm_count_fast[64];
-std::atomic<uint64_t> configured_fast[64];
+std::atomic<int> sm_count_fast[MAX_DEVICES];
+std::atomic<uint64_t> configured_fast[MAX_DEVICES];
 
 int sm_count_of(int device) {
-  if (device < 0) return 148;
-  if (const int known = sm_count_fast[device & 63].load(std::memory_order_relaxed)) return known;
+  if (device < 0 || device >= MAX_DEVICES) return 148;
+  if (const int known = sm_count_fast[device].load(std::memory_order_relaxed)) return known;
   std::lock_guard<std::mutex> lock(device_mutex);
-  DeviceInfo& info = devices[device & 63];
+  DeviceInfo& info = devices[device];
   if (!info.sm_count) {
     int count = 0;
     if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
       count = 148;
     info.sm_count = count;
   }
-  sm_count_fast[device & 63].store(info.sm_count, std::memory_order_relaxed);
+  sm_count_fast[device].store(info.sm_count, std::memory_order_relaxed);
   return info.sm_count;
 }
 
 int ensure_configured(int device, int variant, int smem_bytes) {
   const uint64_t bit = 1ull << variant;
-  if (configured_fast[device & 63].load(std::memory_order_acquire) & bit) return OG_OK;
+  if (configured_fast[device].load(std::memory_order_acquire) & bit) return OG_OK;
   std::lock_guard<std::mutex> lock(device_mutex);
-  DeviceInfo& info = devices[device & 63];
+  DeviceInfo& info = devices[device];
   if (info.configured & bit) return OG_OK;
   const cudaError_t status = configure_variant(variant, SMEM_LIMIT - 1024);  // static barriers take the rest
   if (status != cudaSuccess)
     return fail(OG_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(status));
   (void)smem_bytes;
   info.configured |= bit;
-  configured_fast[device & 63].fetch_or(bit, std::memory_order_release);
+  configured_fast[device].fetch_or(bit, std::memory_order_release);
   return OG_OK;
 }
 
-// The workspace for one stream-K launch on `device` (allocated on first use;
-// flags start at zero and are matched against a per-launch epoch, so they
-// are never cleared).
-int workspace_for(int device, int sm_count, unsigned epoch, float** partial, int** flags) {
-  std::lock_guard<std::mutex> lock(device_mutex);
-  DeviceInfo& info = devices[device & 63];
-  const int slot = int(epoch % WORKSPACES);
-  if (!info.partial[slot]) {
-    const size_t regions = size_t(sm_count) * 4;
+// Allocate `device`'s stream-K workspaces and their guard events, once.
+// Flags start at zero and are matched against a per-launch epoch, so they are
+// never cleared.  The device must be current.  Caller holds device_mutex.
+int allocate_workspaces(DeviceInfo& info, int sm_count) {
+  if (info.partial[WORKSPACES - 1]) return OG_OK;
+  const size_t regions = size_t(sm_count) * 4;
+  for (int slot = 0; slot < WORKSPACES; ++slot) {
+    if (info.partial[slot]) continue;
     void* data = nullptr;
     void* words = nullptr;
+    cudaEvent_t event = nullptr;
     if (cudaMalloc(&data, regions * REGION_BYTES) != cudaSuccess ||
         cudaMalloc(&words, regions * sizeof(int)) != cudaSuccess ||
-        cudaMemset(words, 0, regions * sizeof(int)) != cudaSuccess) {
+        cudaMemset(words, 0, regions * sizeof(int)) != cudaSuccess ||
+        cudaEventCreateWithFlags(&event, cudaEventDisableTiming) != cudaSuccess) {
       cudaGetLastError();
       if (data) cudaFree(data);
       if (words) cudaFree(words);
       return fail(OG_ERR_LAUNCH, "cannot allocate the %zu-byte stream-K workspace", regions * REGION_BYTES);
     }
-    info.partial[slot] = static_cast<float*>(data);
     info.flags[slot] = static_cast<int*>(words);
+    info.released[slot] = event;
+    info.partial[slot] = static_cast<float*>(data);
+  }
+  return OG_OK;
+}
+
+// Take the next workspace of `device` for a stream-K launch on `stream`:
+// returns its buffers and this launch's tag, after making `stream` wait for
+// the slot's previous user.  `*slot_out` is handed to release_workspace once
+// the kernel is enqueued.
+int take_workspace(int device, int sm_count, cudaStream_t stream, float** partial, int** flags, int* tag,
+                   int* slot_out) {
+  std::lock_guard<std::mutex> lock(device_mutex);
+  DeviceInfo& info = devices[device];
+  const int ready = allocate_workspaces(info, sm_count);
+  if (ready != OG_OK) return ready;
+  unsigned epoch = ++info.epoch;
+  if ((epoch & 0x7FFFFFFFu) == 0) epoch = ++info.epoch;  // the tag is never 0
+  const int slot = int(epoch % WORKSPACES);
+  if (epoch > unsigned(WORKSPACES) &&
+      cudaStreamWaitEvent(stream, info.released[slot], 0) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(OG_ERR_LAUNCH, "cudaStreamWaitEvent on the stream-K workspace failed");
   }
   *partial = info.partial[slot];
   *flags = info.flags[slot];
+  *tag = int(epoch & 0x7FFFFFFFu);
+  *slot_out = slot;
   return OG_OK;
+}
+
+void release_workspace(int device, int slot, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(device_mutex);
+  if (cudaEventRecord(devices[device].released[slot], stream) != cudaSuccess) cudaGetLastError();
 }
 
 // Stream-K applies when the tiles do not fill a whole number of waves: the
@@ -269,8 +224,8 @@ struct PlanMemo {
 };
 thread_local PlanMemo plan_memo;
 
-int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, const void* sfb,
-                void* c, int device, void* stream, int* status_word, int want_scaled, const float* alpha = nullptr) {
+int launch_impl(const OgGemm* g, const LaunchPointers& io, int device, void* stream, int* status_word,
+                int want_scaled, const float* alpha = nullptr) {
   if (!g) return fail(OG_ERR_LAUNCH, "null OgGemm");
   if (!plan_memo.valid || std::memcmp(&plan_memo.key, g, sizeof(OgGemm)) != 0) {
     char why[256];
@@ -281,94 +236,27 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
     plan_memo.valid = true;
   }
   const Plan& p = plan_memo.plan;
-  if (g->row != p.variant)
-    return fail(OG_ERR_LAUNCH, "row %d is not the kernel of this OgGemm: bind it first", g->row);
+  char why[320];
   if (want_scaled >= 0 && int(p.format->scaled) != want_scaled)
     return fail(OG_ERR_LAUNCH, "dtype %.16s does not belong to this library", g->dtype);
-  if (!a || !b || !c) return fail(OG_ERR_LAUNCH, "a, b and c must be device pointers, got null");
-  if (p.format->scaled && (!sfa || !sfb))
-    return fail(OG_ERR_LAUNCH, "a block-scaled format takes both sfa and sfb");
-  if (alpha && p.format->out == OUT_S32)
-    return fail(OG_ERR_LAUNCH, "dtype %.16s accumulates integers exactly: its output cannot be scaled", g->dtype);
+  int rc = check_pointers(*g, p, io, alpha, why, sizeof why);
+  if (rc != OG_OK) return fail(rc, "%s", why);
   const int followed = follow_device(device);
   if (followed != OG_OK) return followed;
   const int configured = ensure_configured(device, p.variant, p.smem_bytes);
   if (configured != OG_OK) return configured;
 
   GemmParams params;
-  std::memset(&params, 0, sizeof params);
-  const void* x = p.swap ? b : a;
-  const void* y = p.swap ? a : b;
-  const void* sfx = p.swap ? sfb : sfa;
-  const void* sfy = p.swap ? sfa : sfb;
-  const uint64_t k = uint64_t(p.k);
-  int rc = encode_2d(&params.map_x, x, p.x_map, k, uint64_t(p.rows_m), k * p.x_bits / 8,
-                     uint32_t(p.block_k), 128, CU_TENSOR_MAP_SWIZZLE_128B, p.l2_promo, "the M-side operand");
-  if (rc != OG_OK) return rc;
-  rc = encode_2d(&params.map_y, y, p.y_map, k, uint64_t(p.rows_n), k * p.y_bits / 8,
-                 uint32_t(p.block_k), uint32_t(p.tile_n / p.cta_group), CU_TENSOR_MAP_SWIZZLE_128B,
-                 p.l2_promo, "the N-side operand");
-  if (rc != OG_OK) return rc;
-  const bool c_aligned = (reinterpret_cast<uintptr_t>(c) & 15) == 0;
-  const int epi_staged = p.epi_staged && c_aligned;
-  const int epi_tma = p.epi_tma && c_aligned;
-  if (epi_tma) {
-    const int type = p.format->out == OUT_S32 ? int(CU_TENSOR_MAP_DATA_TYPE_INT32) : int(CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
-    rc = encode_2d(&params.map_d, c, type, uint64_t(g->n), uint64_t(g->m), uint64_t(g->n) * p.out_bytes,
-                   uint32_t(128 / p.out_bytes), 32, CU_TENSOR_MAP_SWIZZLE_128B, 0, "the output");
-    if (rc != OG_OK) return rc;
-  }
-  if (p.format->scaled) {
-    const uint64_t atoms_x = uint64_t(ceil_div(p.rows_m, 128)) * p.k_groups;
-    const uint64_t atoms_y = uint64_t(ceil_div(p.rows_n, 128)) * p.k_groups;
-    rc = encode_2d(&params.map_sfx, sfx, int(CU_TENSOR_MAP_DATA_TYPE_UINT8), 256, 2 * atoms_x, 256, 256,
-                   uint32_t(2 * p.sf_atoms), CU_TENSOR_MAP_SWIZZLE_NONE, 0, "the M-side scales");
-    if (rc != OG_OK) return rc;
-    rc = encode_2d(&params.map_sfy, sfy, int(CU_TENSOR_MAP_DATA_TYPE_UINT8), 256, 2 * atoms_y, 256, 256,
-                   uint32_t(2 * p.sf_atoms), CU_TENSOR_MAP_SWIZZLE_NONE, 0, "the N-side scales");
-    if (rc != OG_OK) return rc;
-  }
-  params.d = c;
-  params.status = status_word;
-  params.wait_limit_ns = (unsigned long long)wait_limit_ns.load();
-  params.rows_m = p.rows_m;
-  params.rows_n = p.rows_n;
-  params.k = p.k;
-  params.ldd = g->n;
-  params.transpose_out = p.swap;
-  params.tile_n = p.tile_n;
-  params.block_k = p.block_k;
-  params.mma_k = p.mma_k;
-  params.k_blocks = p.k_blocks;
-  params.stages = p.stages;
-  params.x_bytes = p.x_bytes;
-  params.y_bytes = p.y_bytes;
-  params.stage_bytes = p.stage_bytes;
-  params.tx_bytes = p.tx_bytes;
-  params.tiles_m = p.tiles_m;
-  params.tiles_n = p.tiles_n;
-  params.num_tiles = p.num_tiles;
-  params.group = p.group;
-  params.idesc = p.idesc;
-  params.acc_slots = p.acc_slots;
-  params.acc_stride = p.acc_stride;
-  params.sf_col = p.sf_col;
-  params.sf_slots = p.sf_slots;
-  params.sf_cols = p.sf_cols;
-  params.tmem_cols = p.tmem_cols;
-  params.epi_staged = epi_staged;
-  params.epi_tma = epi_tma;
-  params.vec_ok = (c_aligned && (int64_t(g->n) * p.out_bytes) % 16 == 0) ? 1 : 0;
-  params.sf_atoms = p.sf_atoms;
-  params.sf_yblocks = p.sf_yblocks;
-  params.k_groups = p.k_groups;
-  if (alpha) {
-    params.scale_out = 1;
-    params.alpha = *alpha;
+  rc = fill_params(p, *g, io, status_word, alpha, current_wait_limit_ns(), &params, why, sizeof why);
+  if (rc != OG_OK) return fail(rc, "%s", why);
+  if (overcredit_next) {  // testing aid: the stage barriers will wait for bytes that never come
+    params.tx_bytes += overcredit_next;
+    overcredit_next = 0;
   }
   static const bool pdl_enabled = [] { const char* e = getenv("OPENGEMM_PDL"); return !(e && e[0] == '0'); }();
   params.pdl = pdl_enabled ? (independent_inputs.load(std::memory_order_relaxed) ? 2 : 1) : 0;
 
+  const cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int sm_count = sm_count_of(device);
   int grid = grid_for(p, sm_count);
   if (g->use_clc && g->split_k < 2) {
@@ -377,11 +265,10 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
     params.use_clc = 1;
     grid = p.num_tiles * p.cta_group;
   }
+  int workspace_slot = -1;
   if (g->split_k >= 2 && use_stream_k(*g, p, grid_for(p, sm_count, true))) {
     grid = grid_for(p, sm_count, true);
-    unsigned epoch = ++launch_epoch;
-    if ((epoch & 0x7FFFFFFFu) == 0) epoch = ++launch_epoch;  // the tag is never 0
-    const int got = workspace_for(device, sm_count, epoch, &params.partial, &params.flags);
+    const int got = take_workspace(device, sm_count, s, &params.partial, &params.flags, &params.epoch, &workspace_slot);
     if (got != OG_OK) return got;
     params.stream_k = 1;
     {
@@ -391,11 +278,10 @@ int launch_impl(const OgGemm* g, const void* a, const void* b, const void* sfa, 
       const int leftover = p.num_tiles % clusters;
       params.sk_clusters = std::min<long long>(clusters, (long long)leftover * std::min<int>(g->split_k, p.k_blocks));
     }
-    params.epoch = int(epoch & 0x7FFFFFFFu);
     params.acc_int = p.format->out == OUT_S32;
   }
-  const cudaError_t launched =
-      launch_variant(p.variant, params, grid, p.smem_bytes, static_cast<cudaStream_t>(stream), params.pdl != 0);
+  const cudaError_t launched = launch_variant(p.variant, params, grid, p.smem_bytes, s, params.pdl != 0);
+  if (workspace_slot >= 0) release_workspace(device, workspace_slot, s);
   if (launched != cudaSuccess)
     return fail(OG_ERR_LAUNCH, "kernel launch failed: %s", cudaGetErrorString(launched));
   return OG_OK;
@@ -423,6 +309,9 @@ int describe_row(bool scaled, int i, OgGemm* out) {
 }
 
 }  // namespace
+
+unsigned long long current_wait_limit_ns() { return (unsigned long long)wait_limit_ns.load(); }
+
 }  // namespace og
 
 using namespace og;
@@ -441,7 +330,7 @@ OG_API int32_t og_mm_launch(const OgGemm* g, const void* a, const void* b, const
                             const void* sfb, void* c, int32_t device, void* stream) {
   (void)sfa;
   (void)sfb;
-  return launch_impl(g, a, b, nullptr, nullptr, c, device, stream, nullptr, 0);
+  return launch_impl(g, LaunchPointers{a, b, nullptr, nullptr, c, nullptr}, device, stream, nullptr, 0);
 }
 
 OG_API int32_t og_smm_abi(void) { return OG_ABI_VERSION; }
@@ -454,7 +343,7 @@ OG_API int32_t og_smm_bind(OgGemm* g) {
 }
 OG_API int32_t og_smm_launch(const OgGemm* g, const void* a, const void* b, const void* sfa,
                              const void* sfb, void* c, int32_t device, void* stream) {
-  return launch_impl(g, a, b, sfa, sfb, c, device, stream, nullptr, 1);
+  return launch_impl(g, LaunchPointers{a, b, sfa, sfb, c, nullptr}, device, stream, nullptr, 1);
 }
 
 OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
@@ -493,13 +382,60 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
 OG_API int32_t og_b200_launch_checked(const OgGemm* g, const void* a, const void* b,
                                       const void* sfa, const void* sfb, void* c, int32_t device,
                                       void* stream, int32_t* status) {
-  return launch_impl(g, a, b, sfa, sfb, c, device, stream, status, -1);
+  return launch_impl(g, LaunchPointers{a, b, sfa, sfb, c, nullptr}, device, stream, status, -1);
 }
 
 OG_API int32_t og_b200_launch_alpha(const OgGemm* g, const void* a, const void* b, const void* sfa,
                                     const void* sfb, void* c, int32_t device, void* stream, float alpha) {
-  return launch_impl(g, a, b, sfa, sfb, c, device, stream, nullptr, -1, &alpha);
+  return launch_impl(g, LaunchPointers{a, b, sfa, sfb, c, nullptr}, device, stream, nullptr, -1, &alpha);
 }
+
+OG_API int32_t og_b200_launch_bias(const OgGemm* g, const void* a, const void* b, const void* sfa,
+                                   const void* sfb, void* c, int32_t device, void* stream, float alpha,
+                                   const void* bias) {
+  const bool scale = alpha != 1.0f;
+  return launch_impl(g, LaunchPointers{a, b, sfa, sfb, c, bias}, device, stream, nullptr, -1, scale ? &alpha : nullptr);
+}
+
+OG_API int32_t og_b200_status(int32_t status_word) {
+  if (status_word == 0) return OG_OK;
+  static const char* const sites[] = {"none", "producer waiting for a free stage", "MMA waiting for a stage's data",
+                                      "MMA waiting for a free accumulator", "epilogue waiting for an accumulator",
+                                      "producer draining", "stream-K finisher waiting for a partial sum",
+                                      "scheduler answer", "tensor-memory allocation"};
+  const int site = status_word & 0xFF;
+  return fail(OG_ERR_TIMEOUT, "a device-side wait gave up: site %d (%s) in CTA %d", site,
+              site >= 0 && site < int(sizeof sites / sizeof sites[0]) ? sites[site] : "unknown", status_word >> 8);
+}
+
+OG_API int32_t og_b200_prepare_device(int32_t device) {
+  const int followed = follow_device(device);
+  if (followed != OG_OK) return followed;
+  for (int variant = 0; variant < 20; ++variant) {
+    const int configured = ensure_configured(device, variant, 0);
+    if (configured != OG_OK) return configured;
+  }
+  const int sm_count = sm_count_of(device);
+  std::lock_guard<std::mutex> lock(device_mutex);
+  return allocate_workspaces(devices[device], sm_count);
+}
+
+OG_API int32_t og_b200_tile_order(const OgGemm* g, int32_t* out, int32_t cap) {
+  if (!g || !out) return fail(OG_ERR_BIND, "null argument");
+  Plan p;
+  char why[256];
+  const int status = make_plan(*g, 148, &p, why, sizeof why);
+  if (status != OG_OK) return fail(status, "%s", why);
+  if (cap < 2 * p.num_tiles) return fail(OG_ERR_BIND, "%d tiles need room for %d integers, got %d", p.num_tiles, 2 * p.num_tiles, cap);
+  for (int tile = 0; tile < p.num_tiles; ++tile) {
+    const TileCoord t = tile_coord_of(tile, p.tiles_m, p.tiles_n, p.group, p.walk);
+    out[2 * tile] = t.mi;
+    out[2 * tile + 1] = t.ni;
+  }
+  return p.num_tiles;
+}
+
+OG_API void og_b200_test_overcredit_next_launch(int32_t bytes) { overcredit_next = bytes; }
 
 OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, int32_t cap) {
   if (!g || !out || cap <= 0) return fail(OG_ERR_BIND, "null argument");
@@ -516,12 +452,12 @@ OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, in
       "\"num_tiles\":%d,\"group\":%d,\"idesc\":%u,\"acc_slots\":%d,\"acc_stride\":%d,\"sf_col\":%d,\"sf_slots\":%d,"
       "\"sf_cols\":%d,\"tmem_cols\":%d,\"epi_staged\":%d,\"epi_tma\":%d,\"out_bytes\":%d,\"out\":%d,\"sf_atoms\":%d,\"sf_yblocks\":%d,"
       "\"k_groups\":%d,\"smem_bytes\":%d,\"x_bits\":%d,\"y_bits\":%d,\"x_map\":%d,\"y_map\":%d,\"l2_promo\":%d,"
-      "\"grid\":%d,\"m\":%d,\"n\":%d}",
+      "\"grid\":%d,\"m\":%d,\"n\":%d,\"walk\":%d}",
       int(p.format->scaled), p.variant, p.format->kind, p.cta_group, p.swap, p.rows_m, p.rows_n, p.k, p.tile_m,
       p.tile_n, p.block_k, p.mma_k, p.k_blocks, p.stages, p.x_bytes, p.y_bytes, p.sf_bytes, p.stage_bytes,
       p.tx_bytes, p.tiles_m, p.tiles_n, p.num_tiles, p.group, p.idesc, p.acc_slots, p.acc_stride, p.sf_col,
       p.sf_slots, p.sf_cols, p.tmem_cols, p.epi_staged, p.epi_tma, p.out_bytes, p.format->out, p.sf_atoms, p.sf_yblocks,
-      p.k_groups, p.smem_bytes, p.x_bits, p.y_bits, p.x_map, p.y_map, p.l2_promo, grid, g->m, g->n);
+      p.k_groups, p.smem_bytes, p.x_bits, p.y_bits, p.x_map, p.y_map, p.l2_promo, grid, g->m, g->n, p.walk);
   if (wrote < 0 || wrote >= cap) return fail(OG_ERR_BIND, "the buffer of %d bytes is too small for the description", cap);
   return OG_OK;
 }

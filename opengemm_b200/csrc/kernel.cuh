@@ -24,6 +24,7 @@
 #pragma once
 
 #include "ptx.cuh"
+#include "raster.h"
 
 namespace og {
 
@@ -77,21 +78,16 @@ struct alignas(64) GemmParams {
   int epoch;              // this launch's tag in `flags` (never 0)
   float* partial;         // per epilogue warp: 32 rows x 256 columns of f32 partial sums
   int* flags;             // per epilogue warp: epoch of the partial it last published
+  int walk;               // rasterisation order (og::Walk)
+  int out_f16;            // 2-byte output is IEEE half instead of bfloat16
+  const float* bias;      // float32 [columns of C], added to every row before the store; may be null
 };
 
-struct TileCoord {
-  int mi, ni;
-};
-
-// Tiles are visited in bands `group` tiles wide along N, N fastest inside a
-// band, so concurrently running clusters share X rows and Y rows in L2.
+// Tiles are visited in the order `walk` names (raster.h); the default is bands
+// `group` tiles wide along N, N fastest inside a band, so concurrently running
+// clusters share X rows and Y rows in L2.
 __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile) {
-  const int band_tiles = p.tiles_m * p.group;
-  const int band = tile / band_tiles;
-  const int first = band * p.group;
-  const int width = min(p.group, p.tiles_n - first);
-  const int in_band = tile - band * band_tiles;
-  return {in_band / width, first + in_band % width};
+  return tile_coord_of(tile, p.tiles_m, p.tiles_n, p.group, p.walk);
 }
 
 // One piece of work for a cluster: K blocks [kb0, kb1) of an output tile.
@@ -242,7 +238,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   constexpr int TILE_M = 128 * CTA_GROUP;
 
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4 + 2 * CLC_SLOTS];
+  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4 + 2 * CLC_SLOTS + 1];
   __shared__ __align__(16) uint4 clc_answers[CLC_SLOTS];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -261,10 +257,22 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   const uint32_t bar_acc_empty = bar_acc_full + 16;
   const uint32_t bar_clc_full = bar_acc_empty + 16;
   const uint32_t bar_clc_empty = bar_clc_full + 8 * CLC_SLOTS;
+  const uint32_t bar_tmem = bar_clc_empty + 8 * CLC_SLOTS;  // tensor memory of every CTA of the pair is allocated
 
   const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
 
+  // Set-up is ordered for a short critical path: the tensor maps are requested
+  // first (their fetch overlaps the rest), only the barriers are synchronised
+  // on, and the producer starts loading while warp 1 is still allocating
+  // tensor memory - its users wait for that on a barrier of its own.
   if (threadIdx.x == 0) {
+    prefetch_tmap(&params.map_x);
+    prefetch_tmap(&params.map_y);
+    if constexpr (SCALED) {
+      prefetch_tmap(&params.map_sfx);
+      prefetch_tmap(&params.map_sfy);
+    }
+    if (p.epi_tma) prefetch_tmap(&params.map_d);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
@@ -279,25 +287,22 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         mbar_init(bar_clc_empty + 8 * s, CLC_READERS * CTA_GROUP);
       }
     }
+    mbar_init(bar_tmem, CTA_GROUP);
     abort_flag = 0;
     mbar_init_fence();
-    prefetch_tmap(&params.map_x);
-    prefetch_tmap(&params.map_y);
-    if (p.epi_tma) prefetch_tmap(&params.map_d);
-    if constexpr (SCALED) {
-      prefetch_tmap(&params.map_sfx);
-      prefetch_tmap(&params.map_sfy);
-    }
   }
+  __syncthreads();
+  if constexpr (CTA_GROUP == 2) cluster_sync_all();
   if (warp == 1) {
     tmem_alloc<CTA_GROUP>(smem_u32(&tmem_slot), p.tmem_cols);
     tmem_relinquish<CTA_GROUP>();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) {  // tell this CTA and, in a pair, the other one
+      mbar_arrive(bar_tmem);
+      if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(map_to_cta(bar_tmem, rank ^ 1u));
+    }
   }
-  tc_fence_before_sync();
-  __syncthreads();
-  if constexpr (CTA_GROUP == 2) cluster_sync_all();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = tmem_slot;
   // Programmatic dependent launch: from here on the next kernel in the stream
   // may start its own set-up on SMs this grid leaves free.  Every thread of
   // this grid that touches global memory first waits for the previous grid.
@@ -400,14 +405,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       const bool two_yblocks = p.sf_yblocks == 2;
       const int yb = p.sf_yblocks;
       const int stages = p.stages, block_k = p.block_k, mma_k = p.mma_k, k_total = p.k;
-      const uint32_t idesc = p.idesc, acc_stride = p.acc_stride, sf_base = tmem_base + p.sf_col, sf_cols = p.sf_cols;
+      const uint32_t idesc = p.idesc, acc_stride = p.acc_stride, sf_cols = p.sf_cols;
       const bool two_acc = p.acc_slots == 2, two_sf = p.sf_slots == 2;
       int stage = 0;
       uint32_t phase = 0;
       uint64_t stage_off = 0;  // stage * (stage_bytes >> 4)
       uint32_t sf_slot = 0;
       int tile_idx = 0;
-      bool ok = true;
+      bool ok = mbar_wait(bar_tmem, 0, ctx, SITE_TMEM_READY);  // both CTAs' allocations
+      tc_fence_after_sync();
+      const uint32_t tmem_base = tmem_slot;
+      const uint32_t sf_base = tmem_base + p.sf_col;
       WorkIter work(p, cluster_id, num_clusters);
       if (p.use_clc) work.enable_clc(clc_state(false, true), CTA_GROUP);
       Work w;
@@ -495,9 +503,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     const int tile_n = p.tile_n, rows_m = p.rows_m, rows_n = p.rows_n, ldd = p.ldd;
     const bool staged = p.epi_staged != 0, transpose_out = p.transpose_out != 0, vec_ok = p.vec_ok != 0;
     uint8_t* const out = static_cast<uint8_t*>(p.d);
-    const bool scale_out = p.scale_out != 0;  // scaled output takes the general loop below
+    const bool scale_out = p.scale_out != 0;  // scaled or biased output takes the general loop below
     const float alpha = p.alpha;
+    const float* const bias = p.bias;
+    const bool out_f16 = p.out_f16 != 0;
+    auto pack2 = [&](uint32_t lo, uint32_t hi) {
+      return out_f16 ? pack_f16x2(__uint_as_float(lo), __uint_as_float(hi))
+                     : pack_bf16x2(__uint_as_float(lo), __uint_as_float(hi));
+    };
     int tile_idx = 0;
+    const bool allocated = mbar_wait(bar_tmem, 0, ctx, SITE_TMEM_READY);
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
     // Stream-K bookkeeping: this warp's region of the partial-sum workspace
     // and its neighbour's (the same warp of the next cluster).
     const int my_region = (cluster_id * CTA_GROUP + int(rank)) * 4 + quarter;
@@ -505,14 +522,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     WorkIter work(p, cluster_id, num_clusters);
     if (p.use_clc) work.enable_clc(clc_state(false, lane == 0), CTA_GROUP);
     Work w;
-    for (; work.next(w); ++tile_idx) {
+    for (; __all_sync(0xFFFFFFFFu, allocated) && work.next(w); ++tile_idx) {
       const TileCoord t = tile_coord(p, w.tile);
       const bool contributes = w.kb0 > 0;          // publish partial sums instead of output
       const bool finishes = !contributes && w.kb1 < p.k_blocks;  // add the sharers' partials before storing
       const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
       const uint32_t use = (p.acc_slots == 2) ? (tile_idx >> 1) : tile_idx;
+#ifdef OG_EXP_LANE0
+      bool ready = true;
+      if (lane == 0) ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
+      ready = __shfl_sync(0xFFFFFFFFu, int(ready), 0) != 0;
+      if (!ready) break;
+#else
       const bool ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
       if (!__all_sync(0xFFFFFFFFu, ready)) break;
+#endif
       tc_fence_after_sync();
       if (p.pdl && !touched_memory) pdl_wait_prior_grids();
       touched_memory = true;
@@ -555,9 +579,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       // chunks are stored while the loads of the next chunk are in flight, the
       // last two are packed to bf16 and held in registers, the accumulator is
       // released, and only then are the held chunks stored.
-      bool handed_back = false;
+      bool handed_back = false, handed_back_late = false;
       if constexpr (OUT_BYTES == 2) {
-        if (p.acc_slots == 1 && staged && tile_n == 256 && !contributes && !finishes && !scale_out && row0 < rows_m) {
+        if (p.acc_slots == 1 && staged && tile_n == 256 && !contributes && !finishes && !scale_out && !bias && !out_f16 &&
+            row0 < rows_m) {
           auto pack64 = [](const uint32_t* f, uint32_t* w) {
 #pragma unroll
             for (int u = 0; u < 32; ++u)
@@ -606,6 +631,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           }
         }
         tmem_ld_wait();
+        if (c + CHUNK >= tile_n || col0 + c + CHUNK >= rows_n) {
+          // The last columns are in registers: the accumulator goes back to
+          // the MMA warp before they are converted and stored.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + 8 * slot);
+            else mbar_arrive(bar_acc_empty + 8 * slot);
+          }
+          handed_back_late = true;
+        }
 
         if (finishes) {
           // Partial sums of every cluster that shares this tile.  All loads of
@@ -645,6 +681,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         if (scale_out && !contributes) {  // the finished sum, scaled once; partial sums travel unscaled
 #pragma unroll
           for (int j = 0; j < CHUNK; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+        }
+        if (bias && !contributes) {
+          // One bias value per column of C: along this thread's registers, or
+          // (operands swapped, C written transposed) one value for its whole row.
+          if (!transpose_out) {
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j)
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(bias + min(col0 + c + j, rows_n - 1)));
+          } else {
+            const float mine = __ldg(bias + min(row, rows_m - 1));
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + mine);
+          }
         }
         if (contributes) {
           // Raw accumulators, 16 bytes per lane per vector so a warp writes 512
@@ -686,8 +735,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           } else {
             uint32_t w[32];
 #pragma unroll
-            for (int u = 0; u < 32; ++u)
-              w[u] = pack_bf16x2(__uint_as_float(v[2 * u]), __uint_as_float(v[2 * u + 1]));
+            for (int u = 0; u < 32; ++u) w[u] = pack2(v[2 * u], v[2 * u + 1]);
             store_staged(w, c, width);
           }
         } else if (!transpose_out) {
@@ -706,11 +754,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
 #pragma unroll
                 for (int u = 0; u < CHUNK / 8; ++u)
                   if (8 * u < width)
-                    dst[u] = make_uint4(
-                        pack_bf16x2(__uint_as_float(v[8 * u]), __uint_as_float(v[8 * u + 1])),
-                        pack_bf16x2(__uint_as_float(v[8 * u + 2]), __uint_as_float(v[8 * u + 3])),
-                        pack_bf16x2(__uint_as_float(v[8 * u + 4]), __uint_as_float(v[8 * u + 5])),
-                        pack_bf16x2(__uint_as_float(v[8 * u + 6]), __uint_as_float(v[8 * u + 7])));
+                    dst[u] = make_uint4(pack2(v[8 * u], v[8 * u + 1]), pack2(v[8 * u + 2], v[8 * u + 3]),
+                                        pack2(v[8 * u + 4], v[8 * u + 5]), pack2(v[8 * u + 6], v[8 * u + 7]));
               }
             } else {
 #pragma unroll
@@ -721,7 +766,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
                     reinterpret_cast<uint32_t*>(out)[at] = v[j];
                   else
                     reinterpret_cast<uint16_t*>(out)[at] =
-                        uint16_t(pack_bf16x2(__uint_as_float(v[j]), 0.f) & 0xFFFFu);
+                        uint16_t(pack2(v[j], 0u) & 0xFFFFu);
                 }
               }
             }
@@ -739,23 +784,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
                   reinterpret_cast<uint32_t*>(out)[at] = v[j];
                 else
                   reinterpret_cast<uint16_t*>(out)[at] =
-                      uint16_t(pack_bf16x2(__uint_as_float(v[j]), 0.f) & 0xFFFFu);
+                      uint16_t(pack2(v[j], 0u) & 0xFFFFu);
               }
             }
           }
         }
       }
       if (contributes) {
-        __threadfence();
         __syncwarp();
-        if (lane == 0) *reinterpret_cast<volatile int*>(p.flags + my_region) = p.epoch;
+        if (lane == 0) flag_release(p.flags + my_region, p.epoch);
       }
-      // The accumulator slot is in registers or on its way out: hand it back.
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0 && !handed_back) {
-        if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + 8 * slot);
-        else mbar_arrive(bar_acc_empty + 8 * slot);
+      // A tile that left its loop early (nothing to store, or a give-up) still
+      // hands the accumulator back.
+      if (!handed_back && !handed_back_late) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTA_GROUP == 2) mbar_arrive_cluster(acc_empty_leader + 8 * slot);
+          else mbar_arrive(bar_acc_empty + 8 * slot);
+        }
       }
     }
     // Shared memory may be released once the last TMA stores have read it.
@@ -769,7 +816,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   tc_fence_after_sync();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc<CTA_GROUP>(tmem_base, p.tmem_cols);
+    tmem_dealloc<CTA_GROUP>(tmem_slot, p.tmem_cols);
   }
 }
 

@@ -37,6 +37,7 @@
 #include <cuda_runtime.h>
 
 #include "kernel.cuh"
+#include "launch_common.h"
 #include "plan.h"
 
 namespace og {
@@ -113,34 +114,6 @@ int set_up(int device, PerDevice** out) {
   return OG_OK;
 }
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                              CUtensorMapFloatOOBfill);
-
-int encode(CUtensorMap* out, const void* base, int type, uint64_t dim0, uint64_t dim1, uint64_t stride,
-           uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle, const char* which) {
-  static EncodeFn fn = [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) != cudaSuccess ||
-        result != cudaDriverEntryPointSuccess)
-      return EncodeFn(nullptr);
-    return reinterpret_cast<EncodeFn>(sym);
-  }();
-  if (!fn) return refuse(OG_ERR_TENSORMAP, "cuTensorMapEncodeTiled is not available: no CUDA driver");
-  const cuuint64_t dims[2] = {dim0, dim1};
-  const cuuint64_t strides[1] = {stride};
-  const cuuint32_t box[2] = {box0, box1};
-  const cuuint32_t ones[2] = {1, 1};
-  const CUresult status = fn(out, CUtensorMapDataType(type), 2, const_cast<void*>(base), dims, strides, box, ones,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (status != CUDA_SUCCESS)
-    return refuse(OG_ERR_TENSORMAP, "cuTensorMapEncodeTiled failed for %s (driver error %d)", which, int(status));
-  return OG_OK;
-}
-
 }  // namespace
 }  // namespace og
 
@@ -161,27 +134,16 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
   if (error_out && error_cap > 0) error_out[0] = 0;
   if (!g) return refuse(OG_ERR_LAUNCH, "null OgGemm");
   Plan p;
-  char why[256];
+  char why[320];
   const int planned = make_plan(*g, 148, &p, why, sizeof why);
   if (planned != OG_OK) return refuse(planned, "%s", why);
-  if (g->row != p.variant)
-    return refuse(OG_ERR_LAUNCH, "row %d is not the kernel of this OgGemm: bind it first", g->row);
-  if (!a || !b || !c) return refuse(OG_ERR_LAUNCH, "a, b and c must be device pointers, got null");
-  if (p.format->scaled && (!sfa || !sfb))
-    return refuse(OG_ERR_LAUNCH, "a block-scaled format takes both sfa and sfb");
+  const LaunchPointers io{a, b, sfa, sfb, c, nullptr};
+  int rc = check_pointers(*g, p, io, nullptr, why, sizeof why);
+  if (rc != OG_OK) return refuse(rc, "%s", why);
 
   PerDevice* dev = nullptr;
   const int ready = set_up(device, &dev);
   if (ready != OG_OK) return ready;
-
-  const int clusters = std::max(1, std::min(p.num_tiles, dev->sm_count / p.cta_group));
-  const int grid = clusters * p.cta_group;
-  const int regions = grid * 4;
-  if (regions > MAX_REGIONS)
-    return refuse(OG_ERR_LAUNCH,
-                  "this launch needs %d partial-sum regions (a grid of %d CTAs); the fixed workspace holds %d "
-                  "(grids of at most %d CTAs): use og_mm_launch / og_smm_launch on this device",
-                  regions, grid, MAX_REGIONS, MAX_CTAS);
   {
     std::lock_guard<std::mutex> lock(setup_mutex);
     const uint64_t bit = 1ull << p.variant;
@@ -193,76 +155,25 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
     }
   }
 
+  // The same parameter block as the ordinary launches build (tensor maps from
+  // the shared per-thread cache, the wait limit of og_b200_set_wait_limit_ms).
   GemmParams params;
-  std::memset(&params, 0, sizeof params);
-  const void* x = p.swap ? b : a;
-  const void* y = p.swap ? a : b;
-  const uint64_t k = uint64_t(p.k);
-  int rc = encode(&params.map_x, x, p.x_map, k, uint64_t(p.rows_m), k * p.x_bits / 8, uint32_t(p.block_k), 128,
-                  CU_TENSOR_MAP_SWIZZLE_128B, "the M-side operand");
-  if (rc != OG_OK) return rc;
-  rc = encode(&params.map_y, y, p.y_map, k, uint64_t(p.rows_n), k * p.y_bits / 8, uint32_t(p.block_k),
-              uint32_t(p.tile_n / p.cta_group), CU_TENSOR_MAP_SWIZZLE_128B, "the N-side operand");
-  if (rc != OG_OK) return rc;
-  const bool c_aligned = (reinterpret_cast<uintptr_t>(c) & 15) == 0;
-  const int epi_staged = p.epi_staged && c_aligned;
-  const int epi_tma = p.epi_tma && c_aligned;
-  if (epi_tma) {
-    const int type = p.format->out == OUT_S32 ? int(CU_TENSOR_MAP_DATA_TYPE_INT32) : int(CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
-    rc = encode(&params.map_d, c, type, uint64_t(g->n), uint64_t(g->m), uint64_t(g->n) * p.out_bytes,
-                uint32_t(128 / p.out_bytes), 32, CU_TENSOR_MAP_SWIZZLE_128B, "the output");
-    if (rc != OG_OK) return rc;
-  }
-  if (p.format->scaled) {
-    const uint64_t atoms_x = uint64_t(ceil_div(p.rows_m, 128)) * p.k_groups;
-    const uint64_t atoms_y = uint64_t(ceil_div(p.rows_n, 128)) * p.k_groups;
-    rc = encode(&params.map_sfx, p.swap ? sfb : sfa, int(CU_TENSOR_MAP_DATA_TYPE_UINT8), 256, 2 * atoms_x, 256,
-                256, uint32_t(2 * p.sf_atoms), CU_TENSOR_MAP_SWIZZLE_NONE, "the M-side scales");
-    if (rc != OG_OK) return rc;
-    rc = encode(&params.map_sfy, p.swap ? sfa : sfb, int(CU_TENSOR_MAP_DATA_TYPE_UINT8), 256, 2 * atoms_y, 256,
-                256, uint32_t(2 * p.sf_atoms), CU_TENSOR_MAP_SWIZZLE_NONE, "the N-side scales");
-    if (rc != OG_OK) return rc;
-  }
-  params.d = c;
-  params.status = nullptr;
-  params.wait_limit_ns = 2000ull * 1000 * 1000;
-  params.rows_m = p.rows_m;
-  params.rows_n = p.rows_n;
-  params.k = p.k;
-  params.ldd = g->n;
-  params.transpose_out = p.swap;
-  params.tile_n = p.tile_n;
-  params.block_k = p.block_k;
-  params.mma_k = p.mma_k;
-  params.k_blocks = p.k_blocks;
-  params.stages = p.stages;
-  params.x_bytes = p.x_bytes;
-  params.y_bytes = p.y_bytes;
-  params.stage_bytes = p.stage_bytes;
-  params.tx_bytes = p.tx_bytes;
-  params.tiles_m = p.tiles_m;
-  params.tiles_n = p.tiles_n;
-  params.num_tiles = p.num_tiles;
-  params.group = p.group;
-  params.idesc = p.idesc;
-  params.acc_slots = p.acc_slots;
-  params.acc_stride = p.acc_stride;
-  params.sf_col = p.sf_col;
-  params.sf_slots = p.sf_slots;
-  params.sf_cols = p.sf_cols;
-  params.tmem_cols = p.tmem_cols;
-  params.epi_staged = epi_staged;
-  params.epi_tma = epi_tma;
-  params.vec_ok = (c_aligned && (int64_t(g->n) * p.out_bytes) % 16 == 0) ? 1 : 0;
-  params.sf_atoms = p.sf_atoms;
-  params.sf_yblocks = p.sf_yblocks;
-  params.k_groups = p.k_groups;
+  rc = fill_params(p, *g, io, nullptr, nullptr, current_wait_limit_ns(), &params, why, sizeof why);
+  if (rc != OG_OK) return refuse(rc, "%s", why);
 
-  // Stream-K wherever every cluster gets at least a tile's worth of K blocks
-  // and the tiles do not already fill whole waves; otherwise the plain
-  // schedule, which needs no workspace at all.
+  // Stream-K wherever the tiles leave a partial wave that can be cut along K;
+  // otherwise the plain schedule, which touches no workspace at all (and is
+  // therefore never refused for its size).
   const cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (p.num_tiles > clusters && p.num_tiles % clusters != 0) {
+  const int clusters = std::max(1, std::min(p.num_tiles, dev->sm_count / p.cta_group));
+  const int grid = clusters * p.cta_group;
+  if (p.num_tiles > clusters && p.num_tiles % clusters != 0 && p.k_blocks > 1) {
+    const int regions = grid * 4;
+    if (regions > MAX_REGIONS)
+      return refuse(OG_ERR_LAUNCH,
+                    "this launch needs %d partial-sum regions (a grid of %d CTAs); the fixed workspace holds %d "
+                    "(grids of at most %d CTAs): use og_mm_launch / og_smm_launch on this device",
+                    regions, grid, MAX_REGIONS, MAX_CTAS);
     unsigned char* flags = dev->workspace + PARTIAL_BYTES;
     // The flag words must not carry a previous call's tags into this one.
     const cudaError_t cleared = cudaMemsetAsync(flags, 0, size_t(regions) * sizeof(int), s);
@@ -280,6 +191,8 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
     params.partial = reinterpret_cast<float*>(dev->workspace);
     params.flags = reinterpret_cast<int*>(flags);
   }
+  // No programmatic overlap with the previous kernel: two of these calls must
+  // never run at once, they share the workspace.
   const cudaError_t launched = (p.variant < 8 || p.variant >= 14) ? launch_dense(p.variant, params, grid, p.smem_bytes, s, false)
                                              : launch_scaled(p.variant, params, grid, p.smem_bytes, s, false);
   if (launched != cudaSuccess) return refuse(OG_ERR_LAUNCH, "kernel launch failed: %s", cudaGetErrorString(launched));

@@ -19,7 +19,7 @@
 
 namespace og {
 
-enum OutType { OUT_F32 = 0, OUT_S32 = 1, OUT_BF16 = 2 };
+enum OutType { OUT_F32 = 0, OUT_S32 = 1, OUT_BF16 = 2, OUT_F16 = 3 };
 
 // Tensor-map element types, numbered like CUtensorMapDataType so this header
 // needs no CUDA include.
@@ -89,6 +89,16 @@ constexpr Format FORMATS[] = {
     {"e2m3.bf16", false, "e2m3", "e2m3", 3, OUT_BF16, 0, 0},
     {"e2m1.bf16", false, "e2m1", "e2m1", 3, OUT_BF16, 0, 0},
     {"e4m3xe5m2.bf16", false, "e4m3", "e5m2", 3, OUT_BF16, 0, 0},
+    // ... or to IEEE half ("<format>.f16"), through the same kernels.
+    {"bf16.f16", false, "bf16", "bf16", 0, OUT_F16, 0, 0},
+    {"f16.f16", false, "f16", "f16", 0, OUT_F16, 0, 0},
+    {"tf32.f16", false, "tf32", "tf32", 1, OUT_F16, 0, 0},
+    {"e4m3.f16", false, "e4m3", "e4m3", 3, OUT_F16, 0, 0},
+    {"e5m2.f16", false, "e5m2", "e5m2", 3, OUT_F16, 0, 0},
+    {"e3m2.f16", false, "e3m2", "e3m2", 3, OUT_F16, 0, 0},
+    {"e2m3.f16", false, "e2m3", "e2m3", 3, OUT_F16, 0, 0},
+    {"e2m1.f16", false, "e2m1", "e2m1", 3, OUT_F16, 0, 0},
+    {"e4m3xe5m2.f16", false, "e4m3", "e5m2", 3, OUT_F16, 0, 0},
 };
 constexpr int NUM_REFERENCE_FORMATS = 14;  // the leading rows are the reference's fourteen
 constexpr int NUM_FORMATS = sizeof(FORMATS) / sizeof(FORMATS[0]);
@@ -108,13 +118,15 @@ inline const Format* format_named(const char (&dtype)[16]) {
 // Everything the launcher needs beyond pointers: filled by make_plan.
 struct Plan {
   const Format* format = nullptr;
-  int variant = -1;  // which compiled kernel: kind * 2 + (cta_group - 1); 14 + ... for dense formats with bf16 output
+  int variant = -1;  // which compiled kernel: kind * 2 + (cta_group - 1); 14 + ... for dense formats with 2-byte output
   int cta_group = 1;
   int swap = 0;
   int rows_m = 0, rows_n = 0, k = 0;  // MMA-side extents (after swap)
   int tile_m = 128, tile_n = 128, block_k = 64, mma_k = 16, k_blocks = 0, stages = 0;
   int x_bytes = 0, y_bytes = 0, sf_bytes = 0, stage_bytes = 0, tx_bytes = 0;
   int tiles_m = 0, tiles_n = 0, num_tiles = 0, group = 1;
+  int walk = 0;       // rasterisation order (raster.h)
+  int x_rows = 128;   // rows of the M-side box one CTA loads per stage
   uint32_t idesc = 0;
   int acc_slots = 2, acc_stride = 0, sf_col = 0, sf_slots = 1, sf_cols = 0, tmem_cols = 32;
   int epi_staged = 0, epi_tma = 0, out_bytes = 4;
@@ -184,7 +196,7 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
   p.cta_group = g.use_2cta ? 2 : 1;
   p.swap = g.swap_ab ? 1 : 0;
   p.variant = f->kind * 2 + (p.cta_group - 1);
-  if (!f->scaled && f->out == OUT_BF16)  // kinds 0, 1, 3 (no integer kind) -> 14..19
+  if (!f->scaled && (f->out == OUT_BF16 || f->out == OUT_F16))  // kinds 0, 1, 3 (no integer kind) -> 14..19
     p.variant = 14 + (f->kind == 3 ? 2 : f->kind) * 2 + (p.cta_group - 1);
   const Element* ea = element(f->a);
   const Element* eb = element(f->b);
@@ -220,7 +232,7 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
   const int y_tx = y_rows * p.block_k * (packed4 ? 4 : p.y_bits) / 8;
   p.tx_bytes = p.cta_group * (x_tx + y_tx + p.sf_bytes);
 
-  p.out_bytes = f->out == OUT_BF16 ? 2 : 4;
+  p.out_bytes = (f->out == OUT_BF16 || f->out == OUT_F16) ? 2 : 4;
   const int64_t ldd = g.n;              // C is [m, n] row-major whichever way the MMA runs
   p.epi_staged = (!g.epi_direct && !p.swap && (ldd * p.out_bytes) % 16 == 0) ? 1 : 0;
   p.tiles_m = ceil_div(p.rows_m, p.tile_m);
@@ -249,7 +261,12 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
     return OG_ERR_NO_KERNEL;
   }
 
-  p.group = std::max(1, std::min<int>(g.supergroup > 0 ? g.supergroup : 8, p.tiles_n));
+  p.walk = (g.walk >= 0 && g.walk <= 4) ? g.walk : 0;
+  {
+    // Bands run along N, except in the row-band walk, where they run along M.
+    const int extent = p.walk == 4 ? p.tiles_m : p.tiles_n;
+    p.group = std::max(1, std::min<int>(g.supergroup > 0 ? g.supergroup : 8, extent));
+  }
   p.l2_promo = g.l2_promo;
 
   const uint32_t n_field = uint32_t(p.tile_n >> 3) << 17;

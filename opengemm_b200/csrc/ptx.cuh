@@ -37,6 +37,7 @@ enum WaitSite : int {
   SITE_DRAIN = 5,
   SITE_PARTIAL_FLAG = 6,
   SITE_CLC = 7,
+  SITE_TMEM_READY = 8,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -112,6 +113,15 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
 constexpr uint32_t WAIT_PARK_NS = 1000000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
+#ifdef OG_EXP_NOHINT
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
@@ -119,6 +129,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(done)
       : "r"(bar), "r"(parity), "r"(WAIT_PARK_NS)
       : "memory");
+#endif
   return done != 0;
 }
 
@@ -134,19 +145,25 @@ struct WaitCtx {
 // Wait for the phase with this parity to complete.  Returns false when the
 // limit ran out, or when another role of this CTA already gave up; the
 // caller then leaves its loop and heads for the common teardown.
+//
+// The waits next to the data (a stage's full / empty barrier, a scheduler
+// answer) give up after the limit; the waits for a whole accumulator, which
+// sit behind an entire K loop of those, allow twice as long, so that a stall
+// is reported where it arose rather than where it was felt.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           int site) {
 #pragma unroll 1
   for (int spin = 0; spin < 64; ++spin)
     if (mbar_try_wait(bar, parity)) return true;
   const uint64_t start = global_timer_ns();
+  const uint64_t limit = (site == SITE_EPI_ACC_FULL || site == SITE_MMA_ACC_EMPTY) ? 2 * ctx.limit_ns : ctx.limit_ns;
 #pragma unroll 1
   while (true) {
 #pragma unroll 1
     for (int spin = 0; spin < 32; ++spin)
       if (mbar_try_wait(bar, parity)) return true;
     if (*ctx.abort_flag) return false;
-    if (global_timer_ns() - start > ctx.limit_ns) {
+    if (global_timer_ns() - start > limit) {
       *ctx.abort_flag = 1;
       if (ctx.status) atomicCAS(ctx.status, 0, site | (int(blockIdx.x) << 8));
       return false;
@@ -154,14 +171,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   }
 }
 
+// Publish `value` in a global flag word after this warp's earlier global
+// stores: the warp has synchronised (the caller's __syncwarp), so lane 0's
+// release store orders all of them before the flag for any thread of the GPU
+// that reads the flag with acquire semantics.
+__device__ __forceinline__ void flag_release(int* flag, int value) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+
+__device__ __forceinline__ int flag_acquire(const int* flag) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+  return v;
+}
+
 // Wait (whole warp) until a global flag word equals `want`: lane 0 polls, the
 // others join it.  Bounded like mbar_wait; false means give up.
 __device__ __forceinline__ bool wait_flag(const int* flag, int want, const WaitCtx& ctx) {
   int ok = 1;
   if ((threadIdx.x & 31) == 0) {
-    const volatile int* f = flag;
     const uint64_t start = global_timer_ns();
-    while (*f != want) {
+    while (flag_acquire(flag) != want) {
       if (*ctx.abort_flag || global_timer_ns() - start > ctx.limit_ns) {
         if (!*ctx.abort_flag) {
           *ctx.abort_flag = 1;
@@ -171,9 +201,8 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int want, const WaitC
         break;
       }
     }
-    __threadfence();
   }
-  ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+  ok = __shfl_sync(0xFFFFFFFFu, ok, 0);  // also orders the other lanes' loads after lane 0's acquire
   return ok != 0;
 }
 
@@ -465,6 +494,12 @@ __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, uint32_t* v) {
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t v;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(v) : "f"(hi), "f"(lo));
+  return v;
+}
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t v;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(v) : "f"(hi), "f"(lo));
   return v;
 }
 

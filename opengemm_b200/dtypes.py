@@ -49,28 +49,36 @@ _ROWS = [
 DTYPES = {row[0]: Dtype(*row[1:]) for row in _ROWS}
 
 # An addition with no counterpart in the reference: every dense float format
-# can round its f32 accumulator to bfloat16 on the way out, which halves the
-# bytes of C.  The native library knows these as "<format>.bf16"; `DTYPES`
-# itself stays the reference's fourteen.
+# can round its f32 accumulator to bfloat16 or to IEEE half on the way out,
+# which halves the bytes of C.  The native library knows these as
+# "<format>.bf16" / "<format>.f16"; `DTYPES` itself stays the reference's
+# fourteen.
 BF16_OUT_SUFFIX = ".bf16"
-BF16_OUT = {
-    row[0] + BF16_OUT_SUFFIX: Dtype(row[1], row[2], row[3], row[4], torch.bfloat16, row[6], row[7], row[8])
+NARROW_OUT_SUFFIXES = {torch.bfloat16: ".bf16", torch.float16: ".f16"}
+NARROW_OUT = {
+    row[0] + suffix: Dtype(row[1], row[2], row[3], row[4], out, row[6], row[7], row[8])
     for row in _ROWS
     if row[1] == "mm" and row[5] is torch.float32
+    for out, suffix in NARROW_OUT_SUFFIXES.items()
 }
+BF16_OUT = {name: d for name, d in NARROW_OUT.items() if name.endswith(BF16_OUT_SUFFIX)}
 
 
 def lookup(name):
-    """The `Dtype` of one of the fourteen formats or of its bfloat16-output variant."""
-    found = DTYPES.get(name) or BF16_OUT.get(name)
+    """The `Dtype` of one of the fourteen formats or of a 2-byte-output variant."""
+    found = DTYPES.get(name) or NARROW_OUT.get(name)
     if found is None:
-        raise TypeError(f"{name} is not a format this build serves; have {list(DTYPES)} (+ '{BF16_OUT_SUFFIX}' on dense float formats)")
+        raise TypeError(f"{name} is not a format this build serves; have {list(DTYPES)} "
+                        f"(+ {' / '.join(map(repr, NARROW_OUT_SUFFIXES.values()))} on dense float formats)")
     return found
 
 
 def base_name(name):
     """The reference format a name belongs to ("e4m3.bf16" -> "e4m3")."""
-    return name[: -len(BF16_OUT_SUFFIX)] if name.endswith(BF16_OUT_SUFFIX) else name
+    for suffix in NARROW_OUT_SUFFIXES.values():
+        if name.endswith(suffix):
+            return name[: -len(suffix)]
+    return name
 
 # Dense formats torch can name by dtype alone: both operands alike and not
 # uint8, which carries four different elements.

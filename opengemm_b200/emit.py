@@ -36,7 +36,7 @@ KIND_NAMES = ["KIND_F16", "KIND_TF32", "KIND_I8", "KIND_F8F6F4", "KIND_MXF8F6F4"
 FIXED_FIELDS = (
     "rows_m", "rows_n", "k", "tile_n", "block_k", "mma_k", "k_blocks", "stages", "x_bytes", "y_bytes",
     "stage_bytes", "tx_bytes", "tiles_m", "tiles_n", "num_tiles", "group", "idesc", "acc_slots", "acc_stride",
-    "sf_col", "sf_slots", "sf_cols", "tmem_cols", "sf_atoms", "sf_yblocks", "k_groups",
+    "sf_col", "sf_slots", "sf_cols", "tmem_cols", "sf_atoms", "sf_yblocks", "k_groups", "walk",
 )
 
 
@@ -187,6 +187,8 @@ def emit(name, m, n, k, config, stem):
         + "#pragma once\n#include <algorithm>\n#include <cstdint>\n#include <cstring>\n#include <cuda.h>\n#include <cuda_runtime.h>\n\n"
         + f"#define OG_FIXED_PLAN(p) do {{ {fixed} }} while (0)\n\n"
         + _strip((CSRC / "ptx.cuh").read_text())
+        + "\n"
+        + _strip((CSRC / "raster.h").read_text())
         + "\n"
         + _strip((CSRC / "kernel.cuh").read_text())
     )

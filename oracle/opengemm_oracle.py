@@ -457,6 +457,19 @@ def check_north_star(name, got, want):
     return ok, float(excess.max()) if excess.size else 0.0
 
 
+def north_star_floor_users(name, got, want):
+    """How many block-scaled outputs pass `check_north_star` only because of
+    its 2^-20 * max|want| floor: outputs within (1 bf16 ulp + 1e-2 |want| +
+    floor) but outside (1 bf16 ulp + 1e-2 |want|).  Reported beside parity
+    results so the floor's reach is visible; 0 for the other output types."""
+    if FORMATS[name][4] != "bf16":
+        return 0
+    g, w = as_float(name, got), as_float(name, want)
+    bare = np.abs(g - w) - (bf16_ulp(w) + 1e-2 * np.abs(w))
+    floor = 2.0**-20 * (float(np.abs(w).max()) if w.size else 0.0)
+    return int(((bare > 0) & (bare <= floor)).sum())
+
+
 def check_bf16_output(got_bits, want_f32):
     """Acceptance for a dense format whose f32 accumulator is rounded to
     bfloat16 on the way out (an output variant this build adds; the reference
@@ -469,5 +482,26 @@ def check_bf16_output(got_bits, want_f32):
     floor = 2.0**-20 * (float(np.abs(want).max()) if want.size else 0.0)
     ulp = bf16_ulp(want)
     excess = (np.abs(got - want) - floor) / ulp
+    bad = ~(excess <= 1.0)
+    return (not bad.any()), float(np.nanmax(excess)) if excess.size else 0.0
+
+
+def f16_ulp(x):
+    """One IEEE half unit in the last place at |x| (subnormals below 2^-14 share 2^-24)."""
+    x = np.abs(np.asarray(x, dtype=np.float64))
+    e = np.floor(np.log2(np.maximum(x, 2.0**-14)))
+    return 2.0 ** (e - 10)
+
+
+def check_f16_output(got_bits, want_f32):
+    """Acceptance for a dense format whose f32 accumulator is rounded to IEEE
+    half on the way out (an output variant this build adds): every output
+    within one half unit in the last place of the float32 reference, plus
+    2^-20 of the largest |reference| (the same cancellation floor as
+    `check_bf16_output`).  Returns (ok, worst excess in ulps)."""
+    got = np.asarray(got_bits).view(np.float16).astype(np.float64)
+    want = np.asarray(want_f32, dtype=np.float64)
+    floor = 2.0**-20 * (float(np.abs(want).max()) if want.size else 0.0)
+    excess = (np.abs(got - want) - floor) / f16_ulp(want)
     bad = ~(excess <= 1.0)
     return (not bad.any()), float(np.nanmax(excess)) if excess.size else 0.0

@@ -115,10 +115,10 @@ def test_plan_invariants_over_the_shape_suite():
     epilogue only on top of the staged one with 4-byte output."""
     from opengemm_b200 import capi
     from opengemm_b200.configs import heuristic_config, load_shapes
-    from opengemm_b200.dtypes import BF16_OUT, DTYPES, base_name
+    from opengemm_b200.dtypes import DTYPES, NARROW_OUT, base_name
 
     checked = 0
-    for name in list(DTYPES) + ["e4m3.bf16", "bf16.bf16"]:
+    for name in list(DTYPES) + ["e4m3.bf16", "bf16.bf16", "tf32.f16"]:
         for m, n, k in load_shapes():
             try:
                 lib, g = capi.bind(name, m, n, k, heuristic_config(base_name(name), m, n, k))
@@ -135,6 +135,29 @@ def test_plan_invariants_over_the_shape_suite():
             assert p["num_tiles"] == p["tiles_m"] * p["tiles_n"] and 1 <= p["grid"] <= 148
             if p["epi_tma"]:
                 assert p["epi_staged"] and p["out_bytes"] == 4 and p["tile_n"] % 32 == 0
-            assert p["out_bytes"] == (2 if (name in BF16_OUT or DTYPES[base_name(name)].out is torch.bfloat16) else 4)
+            assert p["out_bytes"] == (2 if (name in NARROW_OUT or DTYPES[base_name(name)].out is torch.bfloat16) else 4)
             checked += 1
     assert checked > 1000
+
+
+def test_status_words_become_return_codes_with_a_readable_message():
+    lib = capi.library("mm")
+    assert lib.status(0) == capi.OG_OK
+    assert lib.status(2 | (37 << 8)) == capi.OG_ERR_TIMEOUT
+    assert "site 2" in lib.error() and "CTA 37" in lib.error()
+
+
+def test_devices_beyond_the_table_are_refused_not_aliased():
+    lib, g = capi.bind("bf16", 256, 256, 256, {"use_2cta": False, "output_n": 128})
+    status = lib._launch(byref(g), 1, 1, 0, 0, 1, 64, 0)
+    assert status == capi.OG_ERR_LAUNCH and "out of range" in lib.error()
+
+
+def test_half_output_names_bind_to_the_two_byte_kernels():
+    from opengemm_b200.dtypes import NARROW_OUT, base_name
+
+    assert len(NARROW_OUT) == 18 and sum(name.endswith(".f16") for name in NARROW_OUT) == 9
+    for name in ("bf16.f16", "e4m3xe5m2.f16"):
+        lib, g = capi.bind(name, 512, 768, 1024, heuristic_config(base_name(name), 512, 768, 1024))
+        described = lib.describe(g)
+        assert described["out_bytes"] == 2 and 14 <= described["variant"] <= 19 and described["out"] == 3

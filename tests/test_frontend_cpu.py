@@ -197,3 +197,43 @@ def test_suite_report_summary_counts_and_geometric_mean():
     out = summarise(rows)
     assert out["bf16"] == {"measured": 2, "skipped": 1, "incorrect": 1, "geomean_speedup": 1.0, "below_0.95": 1}
     assert out["mxfp4"]["geomean_speedup"] is None and out["mxfp4"]["measured"] == 1
+
+
+def test_build_staleness_is_by_content_and_the_cache_follows_the_environment(tmp_path, monkeypatch):
+    """The in-tree library is current while its stamp matches the sources'
+    content (touching a file changes nothing; another digest does), and the
+    cache location and the JIT switch follow the reference's environment
+    variables (opengemm/python/build.py:21-24,104-125)."""
+    import json
+    import os
+
+    from opengemm_b200 import build
+
+    assert not build.stale()
+    header = build.CSRC / "raster.h"
+    before = header.stat()
+    os.utime(header, None)                       # a newer modification time, same content
+    try:
+        assert not build.stale()
+    finally:
+        os.utime(header, (before.st_atime, before.st_mtime))
+    stamp = build.LIB_DIR / "stamp.json"
+    saved = stamp.read_text()
+    try:
+        stamp.write_text(json.dumps({"sources": "0" * 16}))
+        assert build.stale()
+    finally:
+        stamp.write_text(saved)
+    monkeypatch.setenv("OPENGEMM_CACHE", str(tmp_path / "cache"))
+    assert build.cache_dir() == tmp_path / "cache"
+    monkeypatch.delenv("OPENGEMM_CACHE")
+    monkeypatch.setenv("XDG_CACHE_HOME", str(tmp_path / "xdg"))
+    assert build.cache_dir() == tmp_path / "xdg" / "opengemm_b200"
+    # OPENGEMM_JIT sets the in-tree library aside for the cached one of this exact build
+    monkeypatch.setenv("OPENGEMM_JIT", "1")
+    expected = build.cache_dir() / build.build_hash() / build.LIB_NAME
+    expected.parent.mkdir(parents=True)
+    expected.write_bytes(b"placeholder")        # present already: nothing is compiled
+    assert build.library_path("mm") == expected
+    monkeypatch.setenv("OPENGEMM_LIB_MM", "/somewhere/else.so")
+    assert str(build.library_path("mm")) == "/somewhere/else.so"

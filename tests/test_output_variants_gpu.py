@@ -1,8 +1,11 @@
 """Output variants this build adds to the reference's GEMM: dense float formats
-with the accumulator rounded to bfloat16 on the way out ("<format>.bf16",
-`gemm(..., out_dtype=torch.bfloat16)`), checked against the oracle's float32
-product to one bfloat16 ulp; and an output scale factor (`gemm(..., alpha=)`,
-og_b200_launch_alpha), checked against the oracle's product times alpha."""
+with the accumulator rounded to bfloat16 or IEEE half on the way out
+("<format>.bf16" / "<format>.f16", `gemm(..., out_dtype=)`), checked against
+the oracle's float32 product to one unit in the last place of the output
+type; an output scale factor (`gemm(..., alpha=)`, og_b200_launch_alpha),
+checked against the oracle's product times alpha; and a per-column bias
+(`gemm(..., bias=)`, og_b200_launch_bias), checked against alpha x product +
+bias computed from the oracle's float32 product."""
 
 import numpy as np
 import pytest
@@ -133,3 +136,109 @@ def test_alpha_through_gemm_and_refusal_for_integers():
     lib, g = capi.bind("s8", 128, 128, 128, heuristic_config("s8", 128, 128, 128))
     with pytest.raises(RuntimeError, match="cannot be scaled"):
         lib.launch_alpha(g, i8, i8, None, None, torch.empty((128, 128), device="cuda", dtype=torch.int32), 2.0)
+
+
+def _half_run(case, name, config):
+    m, n, k = case["m"], case["n"], case["k"]
+    d = og.dtypes.lookup(name)
+    lib, g = capi.bind(name, m, n, k, config)
+    out = torch.empty((m, n), device="cuda", dtype=torch.float16)
+    out.view(torch.uint8).fill_(0x7B)  # 0x7b7b is a large finite half
+    lib.launch(g, to_device(case["a"], d.a), to_device(case["b"], d.b), None, None, out)
+    torch.cuda.synchronize()
+    return out.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("base", ["bf16", "f16", "tf32", "e4m3", "e2m3"])
+@pytest.mark.parametrize("shape", [(300, 520, 768), (2304, 2560, 1024), (77, 33, 128)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("plan", PLANS, ids=lambda p: "default" if p is None else "-".join(f"{k}{int(v)}" for k, v in p.items()))
+def test_f16_output_is_the_rounded_f32_product(base, shape, plan):
+    m, n, k = shape
+    case = make_case(base, m, n, k, seed=22)
+    config = heuristic_config(base, m, n, k)
+    if plan:
+        config.update(plan, cluster_m=2 if plan.get("use_2cta") else 1)
+    got = _half_run(case, base + ".f16", config)
+    ok, worst = ora.check_f16_output(got, oracle_of(case))
+    assert ok, f"{base}.f16 {m}x{n}x{k}: {worst:.2f} half ulps from the float32 product"
+
+
+def test_gemm_takes_a_float16_out_dtype():
+    case = make_case("bf16", 256, 384, 512, seed=4)
+    a, b = to_device(case["a"], torch.bfloat16), to_device(case["b"], torch.bfloat16)
+    c = og.gemm(a, b, out_dtype=torch.float16)
+    assert c.dtype is torch.float16 and c.shape == (256, 384)
+    torch.cuda.synchronize()
+    ok, worst = ora.check_f16_output(c.view(torch.int16).cpu().numpy().view(np.uint16), oracle_of(case))
+    assert ok, worst
+
+
+def _biased_case(name, m, n, k, config, alpha, variant=""):
+    """One GEMM with alpha and a per-column bias; returns (output as numpy, alpha x product + bias in float32)."""
+    case = make_case(name, m, n, k, seed=44)
+    d = og.dtypes.lookup(name + variant)
+    lib, g = capi.bind(name + variant, m, n, k, config)
+    scaled = d.impl == "smm"
+    rng = np.random.default_rng(9)
+    bias = (rng.standard_normal(n) * 3).astype(np.float32)
+    out = torch.empty((m, n), device="cuda", dtype=d.out)
+    out.view(torch.uint8).fill_(0x7B)
+    lib.launch_bias(g, to_device(case["a"], d.a), to_device(case["b"], d.b),
+                    to_device(case["sfa"], d.sf) if scaled else None, to_device(case["sfb"], d.sf) if scaled else None,
+                    out, alpha, torch.from_numpy(bias).cuda())
+    torch.cuda.synchronize()
+    fa = ora.dequantize(name, case["a"], case.get("sfa_raw"), k, "a").astype(np.float32)
+    fb = ora.dequantize(name, case["b"], case.get("sfb_raw"), k, "b").astype(np.float32)
+    want = (fa @ fb.T).astype(np.float32) * np.float32(alpha) + bias[None, :]
+    if d.out in (torch.bfloat16, torch.float16):
+        return out.view(torch.int16).cpu().numpy().view(np.uint16), want
+    return out.cpu().numpy(), want
+
+
+@pytest.mark.parametrize("alpha", [1.0, -0.75])
+@pytest.mark.parametrize("name,shape,knobs", [
+    ("e4m3", (300, 520, 768), {}),
+    ("bf16", (2304, 2560, 1024), dict(use_2cta=True, output_n=256)),   # TMA-store epilogue, several tiles per CTA
+    ("tf32", (77, 33, 128), {}),
+    ("e4m3", (64, 2048, 512), dict(swap_ab=True, use_2cta=False, output_n=64)),  # transposed stores: bias rides the MMA rows
+    ("bf16", (300, 520, 768), dict(use_2cta=False, output_n=96, epi_direct=1)),  # each thread its own row
+    ("bf16", (2304, 2560, 1024), dict(use_2cta=True, output_n=128, split_k=2)),  # stream-K: added once, by the finisher
+], ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else None)
+def test_bias_is_added_to_float32_output(name, shape, knobs, alpha):
+    m, n, k = shape
+    config = heuristic_config(name, m, n, k)
+    config.update(knobs, cluster_m=2 if knobs.get("use_2cta", config["use_2cta"]) else 1)
+    got, want = _biased_case(name, m, n, k, config, alpha)
+    ok, figure = ora.check_north_star(name, got, want)
+    assert ok, f"{name} {m}x{n}x{k} alpha={alpha} + bias: {figure}"
+
+
+@pytest.mark.parametrize("name,variant,knobs", [
+    ("nvfp4", "", dict(use_2cta=True, output_n=256)),   # single accumulator: biased output takes the general loop
+    ("mxfp4", "", dict(use_2cta=False, output_n=128)),
+    ("e4m3", ".bf16", dict(use_2cta=True, output_n=192)),
+    ("bf16", ".f16", dict(use_2cta=True, output_n=256)),
+])
+def test_bias_is_added_to_two_byte_output(name, variant, knobs):
+    m, n, k = 2304, 2568, 1024
+    config = heuristic_config(name, m, n, k)
+    config.update(knobs, cluster_m=2 if knobs["use_2cta"] else 1)
+    got, want = _biased_case(name, m, n, k, config, 0.5, variant)
+    ok, worst = (ora.check_f16_output if variant == ".f16" else ora.check_bf16_output)(got, want)
+    assert ok, f"{name}{variant} bias: {worst:.2f} ulps"
+
+
+def test_bias_through_gemm_and_its_refusals():
+    case = make_case("e4m3", 256, 384, 512, seed=3)
+    a, b = to_device(case["a"], torch.float8_e4m3fn), to_device(case["b"], torch.float8_e4m3fn)
+    bias = torch.linspace(-4, 4, 384, device="cuda")
+    c = og.gemm(a, b, bias=bias, alpha=0.25)
+    torch.cuda.synchronize()
+    want = oracle_of(case) * np.float32(0.25) + bias.cpu().numpy()[None, :]
+    ok, figure = ora.check_north_star("e4m3", c.cpu().numpy(), want)
+    assert ok, figure
+    with pytest.raises(TypeError, match="bias must be"):
+        og.gemm(a, b, bias=bias[:100])
+    i8 = torch.ones((128, 128), device="cuda", dtype=torch.int8)
+    with pytest.raises(TypeError):
+        og.gemm(i8, i8, bias=torch.zeros(128, device="cuda"))

@@ -21,7 +21,7 @@ import torch
 from opengemm_b200 import capi
 from opengemm_b200.dtypes import DTYPES
 from oracle import opengemm_oracle as ora
-from tests.gemm_util import make_case, to_device
+from tests.gemm_util import assert_parity, make_case, to_device
 
 pytestmark = pytest.mark.gpu
 
@@ -81,6 +81,7 @@ def test_no_alloc_launch_matches_the_ordinary_launch(name, shape, knobs):
             assert ok, f"call {call}: outside tolerance by {worst}"
             ok, figure = ora.check_north_star(name, got, want)
             assert ok, f"call {call}: strict bound missed ({figure})"
+        assert_parity(case, got)  # and against the CPU oracle itself, not only kernel against kernel
 
 
 def test_no_alloc_launch_reports_errors_in_the_callers_buffer():
@@ -92,3 +93,52 @@ def test_no_alloc_launch_reports_errors_in_the_callers_buffer():
     g.row = -7
     status = no_alloc(byref(g), 1, 1, 0, 0, 1, 0, 0, message, len(message))
     assert status == capi.OG_ERR_LAUNCH and b"bind it first" in message.value
+
+
+def test_no_alloc_launch_between_ordinary_launches_on_one_stream():
+    """Ordinary launches overlap their neighbours programmatically; the
+    allocation-free one must not, and all three write the same C here: the
+    last writer's result has to be the one left standing, three times over."""
+    name, (m, n, k) = "s8", (2304, 2560, 1024)
+    d = DTYPES[name]
+    config = {"use_2cta": True, "output_n": 128, "swap_ab": False, "epi_direct": 0, "supergroup": 4, "cluster_m": 2}
+    lib, g = capi.bind(name, m, n, k, config)
+    no_alloc = _entry(lib)
+    cases = [make_case(name, m, n, k, seed=s) for s in (1, 2, 3)]
+    operands = [(to_device(c["a"], d.a), to_device(c["b"], d.b)) for c in cases]
+    out = torch.empty((m, n), device="cuda", dtype=d.out)
+    message = ctypes.create_string_buffer(320)
+    for order in ((0, 1, 2), (2, 0, 1)):
+        for position, which in enumerate(order):
+            a, b = operands[which]
+            if position == 1:
+                status = no_alloc(byref(g), a.data_ptr(), b.data_ptr(), 0, 0, out.data_ptr(), 0, capi.raw_stream(0),
+                                  message, len(message))
+                assert status == capi.OG_OK, message.value.decode()
+            else:
+                lib.launch(g, a, b, None, None, out)
+        torch.cuda.synchronize()
+        assert_parity(cases[order[-1]], out.cpu().numpy())
+
+
+def test_no_alloc_launch_honours_the_wait_limit_setting():
+    """The limit set by og_b200_set_wait_limit_ms reaches this entry point too
+    (it shares the parameter block of the ordinary launches): a short limit
+    must not disturb a healthy launch."""
+    name, (m, n, k) = "bf16", (300, 520, 768)
+    d = DTYPES[name]
+    lib, g = capi.bind(name, m, n, k, {"use_2cta": False, "output_n": 64})
+    no_alloc = _entry(lib)
+    case = make_case(name, m, n, k, seed=8)
+    a, b = to_device(case["a"], d.a), to_device(case["b"], d.b)
+    out = torch.empty((m, n), device="cuda", dtype=d.out)
+    message = ctypes.create_string_buffer(320)
+    try:
+        lib.set_wait_limit_ms(50)
+        status = no_alloc(byref(g), a.data_ptr(), b.data_ptr(), 0, 0, out.data_ptr(), 0, capi.raw_stream(0),
+                          message, len(message))
+        torch.cuda.synchronize()
+    finally:
+        lib.set_wait_limit_ms(2000)
+    assert status == capi.OG_OK, message.value.decode()
+    assert_parity(case, out.cpu().numpy())
