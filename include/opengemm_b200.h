@@ -122,6 +122,7 @@ typedef struct {
   int32_t group;     /* rasterisation band width in tiles */
   int32_t stream_k;  /* partial wave cut along K across clusters (split_k >= 2) */
   int32_t use_clc;   /* tiles handed out by cluster launch control; grid = one cluster per tile */
+  int32_t fixed_shape; /* served by a kernel compiled for exactly this tile shape (og_b200_set_fixed_kernels) */
 } OgPlan;
 
 /* Describe how `g` (already bound by og_mm_bind / og_smm_bind) would run on `device`
@@ -156,6 +157,20 @@ OG_API int32_t og_b200_launch_alpha(const OgGemm* g, const void* a, const void* 
 OG_API int32_t og_b200_launch_bias(const OgGemm* g, const void* a, const void* b,
                                    const void* sfa, const void* sfb, void* c, int32_t device,
                                    void* stream, float alpha, const void* bias);
+
+/* Output variant: C leaves block-scaled - quantised along N exactly as the reference's
+ * quantize (opengemm/python/quant.py:99-122) followed by to_blocked (quant.py:82-97) would
+ * quantise a bfloat16 C - so that it can be the A operand of the next block-scaled GEMM
+ * without a round trip through memory in bfloat16.  `out_format` is "nvfp4", "mxfp8" or
+ * "mxfp4"; `c_packed` receives m x n/2 bytes (fp4) or m x n bytes (mxfp8), row-major;
+ * `c_scales` the 128x4 blocked scales (ceil(m/128)*128 x ceil(n/(4*block))*4 bytes; rows past
+ * m are left untouched).  g->dtype must be a block-scaled format or a "<format>.bf16" name;
+ * n a multiple of 64, the tile width a multiple of 64, swap_ab 0.  The reference's
+ * epilogues write bfloat16 or float32 only (opengemm/src/smm/kernel.cuh:374-598). */
+OG_API int32_t og_b200_launch_quantized(const OgGemm* g, const void* a, const void* b,
+                                        const void* sfa, const void* sfb, void* c_packed,
+                                        void* c_scales, int32_t device, void* stream,
+                                        const char* out_format);
 
 /* Do now what launches on `device` do on first use: opt every kernel into its shared
  * memory and allocate the stream-K workspaces.  Call it before capturing launches into
@@ -200,6 +215,13 @@ OG_API const char* og_b200_quantize_error(void);
  * waiting, and only the stores wait - which is the only mode the reference has
  * (opengemm/src/mm/kernel.cuh:209,479-483).  Default 0. */
 OG_API void og_b200_set_independent_inputs(int32_t yes);
+
+/* The hot tile shapes (pairs of CTAs on 256-row tiles, the decode tile) also exist as
+ * kernels compiled for that one shape, with the plan's constants folded in; a launch whose
+ * plan equals one of them runs it, every other launch runs the run-time-planned kernel.
+ * Both compute the same bits.  `yes` = 0 sends every launch to the run-time kernel
+ * (default 1; the environment variable OPENGEMM_FIXED=0 sets the default to 0). */
+OG_API void og_b200_set_fixed_kernels(int32_t yes);
 
 /* Limit of every device-side wait in milliseconds (default 2000).  Waits for a whole
  * accumulator, which sit behind a K loop of the others, allow twice as long. */

@@ -75,7 +75,8 @@ def output(d, m, n, out, device):
     return out
 
 
-def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=None, alpha=None, bias=None):
+def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=None, alpha=None, bias=None,
+         out_format=None):
     """Compute C[M, N] = A[M, K] @ B[N, K].T.
 
     Args:
@@ -97,6 +98,11 @@ def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=N
         bias: a float32 CUDA vector of N values added to every row of C (after
             `alpha`, in float32, before the store; an addition of this build;
             float formats only).
+        out_format: "nvfp4", "mxfp8" or "mxfp4" makes C leave block-scaled
+            along N, bit for bit what `quantize(c.to(bfloat16), out_format)`
+            and `to_blocked` would give, ready to be the `a` of the next
+            block-scaled GEMM (an addition of this build; float formats only,
+            N a multiple of 64).  Returns `(packed, blocked scales)`.
 
     Returns:
         `(M, N)` row-major: float32 for dense formats (bfloat16 with
@@ -104,6 +110,8 @@ def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=N
         for s8 and u8, bfloat16 for block-scaled ones.
     """
     name = dtype_name(a, b, sfa, atype, btype)
+    if out_format is not None:
+        return _gemm_quantized(name, a, b, sfa, sfb, out_format)
     if out_dtype is None and out is not None and out.dtype in NARROW_OUT_SUFFIXES and DTYPES[name].out is torch.float32:
         out_dtype = out.dtype
     if out_dtype is not None and out_dtype is not DTYPES[name].out:
@@ -130,3 +138,35 @@ def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=N
         raise TypeError(f"bias must be a contiguous float32 [{n}] on {a.device}")
     lib.launch_bias(g, a, b, sfa, sfb, out, 1.0 if alpha is None else alpha, bias)
     return out
+
+
+def _gemm_quantized(name, a, b, sfa, sfb, out_format):
+    """gemm() with a block-scaled C: `(packed, blocked scales)`."""
+    if out_format not in ("nvfp4", "mxfp8", "mxfp4"):
+        raise TypeError(f"out_format must be 'nvfp4', 'mxfp8' or 'mxfp4', got {out_format!r}")
+    if DTYPES[name].out is torch.int32:
+        raise TypeError(f"{name} accumulates integers: its output cannot be block-scaled")
+    if DTYPES[name].impl == "mm":
+        name += NARROW_OUT_SUFFIXES[torch.bfloat16]  # the kernels that round the accumulator to bfloat16
+    d, target = lookup(name), DTYPES[out_format]
+    m, n, k = a.size(0), b.size(0), k_of(d, a.size(1))
+    check_operands(d, m, n, k, a, b, sfa, sfb)
+    if n % 64:
+        raise ValueError(f"a block-scaled output needs N to be a multiple of 64, got {n}")
+    lib, g = _bound.get((name, m, n, k, "quantized")) or _bind_quantized(name, m, n, k, a.device)
+    packed = torch.empty((m, extent(target, n)), device=a.device, dtype=target.a)
+    scales = torch.zeros(scale_bytes(target, m, n), device=a.device, dtype=torch.uint8).view(target.sf)
+    lib.launch_quantized(g, a, b, sfa, sfb, packed, scales, out_format)
+    return packed, scales
+
+
+def _bind_quantized(name, m, n, k, device):
+    """The stored configuration, kept off the operand swap and on 64-column tile multiples."""
+    with torch.cuda.device(device):
+        config = dict(resolve_config(base_name(name), m, n, k))
+    if config.get("swap_ab"):
+        config.update(swap_ab=False, use_2cta=m > 128, cluster_m=2 if m > 128 else 1, output_n=128)
+    config["output_n"] = max(64, -(-int(config["output_n"]) // 64) * 64) if config["output_n"] % 64 else config["output_n"]
+    config["output_n"] = min(config["output_n"], 256)
+    _bound[(name, m, n, k, "quantized")] = capi.bind(name, m, n, k, config)
+    return _bound[(name, m, n, k, "quantized")]

@@ -51,7 +51,7 @@ class OgPlan(ctypes.Structure):
         (f, c_int32)
         for f in (
             "cta_group", "tile_m", "tile_n", "block_k", "stages", "swap", "epi_staged", "epi_tma",
-            "acc_slots", "tmem_cols", "smem_bytes", "tiles", "grid", "group", "stream_k", "use_clc",
+            "acc_slots", "tmem_cols", "smem_bytes", "tiles", "grid", "group", "stream_k", "use_clc", "fixed_shape",
         )
     ]
 
@@ -162,6 +162,11 @@ class Library:
             self._tile_order.restype, self._tile_order.argtypes = c_int32, [POINTER(OgGemm), POINTER(c_int32), c_int32]
             self._overcredit = lib.og_b200_test_overcredit_next_launch
             self._overcredit.restype, self._overcredit.argtypes = None, [c_int32]
+            self._quantized = lib.og_b200_launch_quantized
+            self._quantized.restype = c_int32
+            self._quantized.argtypes = [POINTER(OgGemm)] + [c_void_p] * 6 + [c_int32, c_void_p, c_char_p]
+            self._fixed = lib.og_b200_set_fixed_kernels
+            self._fixed.restype, self._fixed.argtypes = None, [c_int32]
         self._kernels = None
 
     def error(self):
@@ -246,6 +251,18 @@ class Library:
         if status != OG_OK:
             raise RuntimeError(self.error())
 
+    def launch_quantized(self, g, a, b, sfa, sfb, packed, scales, out_format):
+        """Like `launch`, with C leaving block-scaled: packed codes into `packed`,
+        128x4 blocked scales into `scales`."""
+        device = a.get_device()
+        status = self._quantized(
+            byref(g), a.data_ptr(), b.data_ptr(),
+            0 if sfa is None else sfa.data_ptr(), 0 if sfb is None else sfb.data_ptr(),
+            packed.data_ptr(), scales.data_ptr(), device, raw_stream(device), out_format.encode(),
+        )
+        if status != OG_OK:
+            raise RuntimeError(self.error())
+
     def status(self, word):
         """OG_OK for a zero status word of `launch_checked`, else OG_ERR_TIMEOUT with
         `error()` naming the wait that gave up."""
@@ -300,6 +317,10 @@ class Library:
     def set_independent_inputs(self, yes):
         """Vouch (or stop vouching) that no earlier kernel of the stream writes a launch's operands."""
         self._independent(int(bool(yes)))
+
+    def set_fixed_kernels(self, yes):
+        """Let launches use the kernels compiled for one tile shape (default), or send all to the run-time kernel."""
+        self._fixed(int(bool(yes)))
 
     def set_wait_limit_ms(self, ms):
         self._set_limit(int(ms))

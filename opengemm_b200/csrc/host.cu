@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include "kernel.cuh"
+#include "kernels_fixed.cuh"
 #include "launch_common.h"
 #include "plan.h"
 
@@ -32,6 +33,16 @@ cudaError_t launch_dense(int variant, const GemmParams& params, int grid, int sm
                          cudaStream_t stream, bool pdl);
 cudaError_t launch_scaled(int variant, const GemmParams& params, int grid, int smem_bytes,
                           cudaStream_t stream, bool pdl);
+
+// Implemented in kernels_fixed_dense.cu and kernels_fixed_scaled.cu.
+extern const FixedKernel FIXED_DENSE[];
+extern const int FIXED_DENSE_COUNT;
+extern const FixedKernel FIXED_SCALED[];
+extern const int FIXED_SCALED_COUNT;
+
+inline const FixedKernel& fixed_kernel(int index) {
+  return index < FIXED_DENSE_COUNT ? FIXED_DENSE[index] : FIXED_SCALED[index - FIXED_DENSE_COUNT];
+}
 
 inline cudaError_t configure_variant(int variant, int smem_bytes) {
   return (variant < 8 || variant >= 14) ? configure_dense(variant, smem_bytes) : configure_scaled(variant, smem_bytes);
@@ -109,6 +120,40 @@ int sm_count_of(int device) {
   }
   sm_count_fast[device].store(info.sm_count, std::memory_order_relaxed);
   return info.sm_count;
+}
+
+// The kernel compiled for exactly this launch's tile shape, if there is one:
+// its index, else -1.  Every value such a kernel has folded in must equal the
+// launch's, and every option it was compiled without must be off.
+std::atomic<int> fixed_kernels_on{[] { const char* e = getenv("OPENGEMM_FIXED"); return (e && e[0] == '0') ? 0 : 1; }()};
+
+int fixed_kernel_for(const Plan& p, const GemmParams& params) {
+  if (!fixed_kernels_on.load(std::memory_order_relaxed)) return -1;
+  if (params.transpose_out || !params.vec_ok || params.use_clc || params.stream_k || params.scale_out ||
+      params.bias || params.out_f16 || params.out_quant || params.walk)
+    return -1;
+  const int epi = params.epi_tma ? 2 : params.epi_staged ? 1 : 0;
+  for (int i = 0; i < FIXED_DENSE_COUNT + FIXED_SCALED_COUNT; ++i) {
+    const FixedKernel& k = fixed_kernel(i);
+    if (k.variant != p.variant || k.tile_n != params.tile_n || k.epi != epi) continue;
+    const TileShape t = tile_shape(p.smem_bits, p.format->scaled ? p.format->sf_block : 0, p.cta_group,
+                                   p.out_bytes, k.tile_n, k.epi);
+    return t.stages == params.stages ? i : -1;
+  }
+  return -1;
+}
+
+std::atomic<uint64_t> fixed_configured_fast[MAX_DEVICES];
+
+int ensure_fixed_configured(int device, int index) {
+  const uint64_t bit = 1ull << index;
+  if (fixed_configured_fast[device].load(std::memory_order_acquire) & bit) return OG_OK;
+  std::lock_guard<std::mutex> lock(device_mutex);
+  const cudaError_t status = fixed_kernel(index).configure(SMEM_LIMIT - 1024);
+  if (status != cudaSuccess)
+    return fail(OG_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(status));
+  fixed_configured_fast[device].fetch_or(bit, std::memory_order_release);
+  return OG_OK;
 }
 
 int ensure_configured(int device, int variant, int smem_bytes) {
@@ -280,7 +325,14 @@ int launch_impl(const OgGemm* g, const LaunchPointers& io, int device, void* str
     }
     params.acc_int = p.format->out == OUT_S32;
   }
-  const cudaError_t launched = launch_variant(p.variant, params, grid, p.smem_bytes, s, params.pdl != 0);
+  const int fixed = fixed_kernel_for(p, params);
+  if (fixed >= 0) {
+    const int ready = ensure_fixed_configured(device, fixed);
+    if (ready != OG_OK) return ready;
+  }
+  const cudaError_t launched =
+      fixed >= 0 ? fixed_kernel(fixed).launch(params, grid, p.smem_bytes, s, params.pdl != 0)
+                 : launch_variant(p.variant, params, grid, p.smem_bytes, s, params.pdl != 0);
   if (workspace_slot >= 0) release_workspace(device, workspace_slot, s);
   if (launched != cudaSuccess)
     return fail(OG_ERR_LAUNCH, "kernel launch failed: %s", cudaGetErrorString(launched));
@@ -376,6 +428,16 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
     out->grid = grid_for(p, sm_count_of(device), true);
     out->stream_k = 1;
   }
+  {
+    // Which kernel a plain launch into a 16-byte aligned C would run.
+    GemmParams probe;
+    std::memset(&probe, 0, sizeof probe);
+    probe.tile_n = p.tile_n, probe.stages = p.stages, probe.epi_staged = p.epi_staged, probe.epi_tma = p.epi_tma;
+    probe.transpose_out = p.swap, probe.walk = p.walk, probe.use_clc = out->use_clc, probe.stream_k = out->stream_k;
+    probe.vec_ok = (int64_t(g->n) * p.out_bytes) % 16 == 0;
+    probe.out_f16 = p.format->out == OUT_F16;
+    out->fixed_shape = fixed_kernel_for(p, probe) >= 0 ? 1 : 0;
+  }
   return OG_OK;
 }
 
@@ -397,6 +459,20 @@ OG_API int32_t og_b200_launch_bias(const OgGemm* g, const void* a, const void* b
   return launch_impl(g, LaunchPointers{a, b, sfa, sfb, c, bias}, device, stream, nullptr, -1, scale ? &alpha : nullptr);
 }
 
+OG_API int32_t og_b200_launch_quantized(const OgGemm* g, const void* a, const void* b, const void* sfa,
+                                        const void* sfb, void* c_packed, void* c_scales, int32_t device,
+                                        void* stream, const char* out_format) {
+  int which = 0;
+  if (out_format && !std::strcmp(out_format, "nvfp4")) which = 1;
+  else if (out_format && !std::strcmp(out_format, "mxfp8")) which = 2;
+  else if (out_format && !std::strcmp(out_format, "mxfp4")) which = 3;
+  else return fail(OG_ERR_LAUNCH, "%.16s is not a block-scaled format: nvfp4, mxfp8 or mxfp4", out_format ? out_format : "(null)");
+  LaunchPointers io{a, b, sfa, sfb, c_packed, nullptr};
+  io.out_quant = which;
+  io.c_scales = c_scales;
+  return launch_impl(g, io, device, stream, nullptr, -1);
+}
+
 OG_API int32_t og_b200_status(int32_t status_word) {
   if (status_word == 0) return OG_OK;
   static const char* const sites[] = {"none", "producer waiting for a free stage", "MMA waiting for a stage's data",
@@ -413,6 +489,10 @@ OG_API int32_t og_b200_prepare_device(int32_t device) {
   if (followed != OG_OK) return followed;
   for (int variant = 0; variant < 20; ++variant) {
     const int configured = ensure_configured(device, variant, 0);
+    if (configured != OG_OK) return configured;
+  }
+  for (int index = 0; index < FIXED_DENSE_COUNT + FIXED_SCALED_COUNT; ++index) {
+    const int configured = ensure_fixed_configured(device, index);
     if (configured != OG_OK) return configured;
   }
   const int sm_count = sm_count_of(device);
@@ -463,6 +543,8 @@ OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, in
 }
 
 OG_API void og_b200_set_independent_inputs(int32_t yes) { independent_inputs.store(yes ? 1 : 0); }
+
+OG_API void og_b200_set_fixed_kernels(int32_t yes) { fixed_kernels_on.store(yes ? 1 : 0); }
 
 OG_API void og_b200_set_wait_limit_ms(int32_t ms) {
   wait_limit_ns.store((long long)std::max(1, (int)ms) * 1000000ll);

@@ -24,7 +24,11 @@
 #pragma once
 
 #include "ptx.cuh"
+#include "quant_math.cuh"
 #include "raster.h"
+#ifndef OG_FIXED_PLAN
+#include "plan.h"
+#endif
 
 namespace og {
 
@@ -81,6 +85,12 @@ struct alignas(64) GemmParams {
   int walk;               // rasterisation order (og::Walk)
   int out_f16;            // 2-byte output is IEEE half instead of bfloat16
   const float* bias;      // float32 [columns of C], added to every row before the store; may be null
+  // Block-scaled output (2-byte-output kernels only): C leaves quantised along
+  // N, ready to be the A operand of the next block-scaled GEMM.  `d` then
+  // receives the packed values and `out_scales` the 128x4 blocked scales.
+  int out_quant;          // 0 off, else 1 + QFormat: 1 nvfp4, 2 mxfp8, 3 mxfp4
+  int out_k_groups;       // 512-byte scale atoms along N of `out_scales`
+  uint8_t* out_scales;
 };
 
 // Tiles are visited in the order `walk` names (raster.h); the default is bands
@@ -222,7 +232,45 @@ struct WorkIter {
   }
 };
 
-template <int KIND, int CTA_GROUP, int OUT_BYTES>
+#ifndef OG_FIXED_PLAN
+// Overwrite, in a local copy of the launch parameters, everything that
+// follows from the tile shape alone with compile-time values (the same
+// tile_shape() the host plans with), and switch off the options a kernel
+// compiled for one shape does not serve: the compiler then folds loop bounds
+// and address arithmetic and drops the unused paths.  The host launches such
+// a kernel only for a plan whose fields equal these (kernels_fixed.cu).
+template <int KIND, int CTA_GROUP, int OUT_BYTES, int FIXED_N, int FIXED_EPI>
+struct FoldedShape {
+  static constexpr int SMEM_BITS = KIND == KIND_F16 ? 16 : KIND == KIND_TF32 ? 32 : (KIND == KIND_MXF4 || KIND == KIND_NVF4) ? 4 : 8;
+  static constexpr int SF_BLOCK = KIND == KIND_NVF4 ? 16 : kind_scaled(KIND) ? 32 : 0;
+#define OG_FOLDED(field) \
+  static constexpr int field = tile_shape(SMEM_BITS, SF_BLOCK, CTA_GROUP, OUT_BYTES, FIXED_N, FIXED_EPI).field
+  OG_FOLDED(tile_n); OG_FOLDED(block_k); OG_FOLDED(mma_k); OG_FOLDED(stages);
+  OG_FOLDED(x_bytes); OG_FOLDED(y_bytes); OG_FOLDED(stage_bytes);
+  OG_FOLDED(acc_slots); OG_FOLDED(acc_stride); OG_FOLDED(sf_col); OG_FOLDED(sf_slots); OG_FOLDED(sf_cols);
+  OG_FOLDED(tmem_cols); OG_FOLDED(sf_atoms); OG_FOLDED(sf_yblocks); OG_FOLDED(epi_staged); OG_FOLDED(epi_tma);
+#undef OG_FOLDED
+};
+
+template <int KIND, int CTA_GROUP, int OUT_BYTES, int FIXED_N, int FIXED_EPI>
+__device__ __forceinline__ void fold_tile_shape(GemmParams& p) {
+  using T = FoldedShape<KIND, CTA_GROUP, OUT_BYTES, FIXED_N, FIXED_EPI>;
+  p.tile_n = T::tile_n, p.block_k = T::block_k, p.mma_k = T::mma_k, p.stages = T::stages;
+  p.x_bytes = T::x_bytes, p.y_bytes = T::y_bytes, p.stage_bytes = T::stage_bytes;
+  p.acc_slots = T::acc_slots, p.acc_stride = T::acc_stride;
+  p.sf_col = T::sf_col, p.sf_slots = T::sf_slots, p.sf_cols = T::sf_cols, p.tmem_cols = T::tmem_cols;
+  p.sf_atoms = T::sf_atoms, p.sf_yblocks = T::sf_yblocks;
+  p.epi_staged = T::epi_staged, p.epi_tma = T::epi_tma;
+  p.transpose_out = 0, p.vec_ok = 1, p.walk = 0;
+  p.use_clc = 0, p.stream_k = 0, p.scale_out = 0, p.out_f16 = 0, p.out_quant = 0;
+  p.bias = nullptr;
+}
+#endif
+
+// FIXED_N == 0: every tile-plan value is read from `params` at run time.
+// FIXED_N != 0: the kernel is compiled for tiles FIXED_N wide with epilogue
+// path FIXED_EPI (0 each thread its own row, 1 staged rows, 2 TMA stores).
+template <int KIND, int CTA_GROUP, int OUT_BYTES, int FIXED_N = 0, int FIXED_EPI = 0>
 __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams params) {
   // `p` is the scalar view of the launch parameters.  A standalone kernel
   // emitted for one shape defines OG_FIXED_PLAN to overwrite the plan fields
@@ -232,7 +280,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   GemmParams p = params;
   OG_FIXED_PLAN(p);
 #else
-  const GemmParams& p = params;
+  GemmParams folded;
+  const GemmParams* view = &params;
+  if constexpr (FIXED_N != 0) {
+    folded = params;
+    fold_tile_shape<KIND, CTA_GROUP, OUT_BYTES, FIXED_N, FIXED_EPI>(folded);
+    view = &folded;
+  }
+  const GemmParams& p = *view;
 #endif
   constexpr bool SCALED = kind_scaled(KIND);
   constexpr int TILE_M = 128 * CTA_GROUP;
@@ -528,15 +583,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       const bool finishes = !contributes && w.kb1 < p.k_blocks;  // add the sharers' partials before storing
       const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
       const uint32_t use = (p.acc_slots == 2) ? (tile_idx >> 1) : tile_idx;
-#ifdef OG_EXP_LANE0
-      bool ready = true;
-      if (lane == 0) ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
-      ready = __shfl_sync(0xFFFFFFFFu, int(ready), 0) != 0;
-      if (!ready) break;
-#else
       const bool ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
       if (!__all_sync(0xFFFFFFFFu, ready)) break;
-#endif
       tc_fence_after_sync();
       if (p.pdl && !touched_memory) pdl_wait_prior_grids();
       touched_memory = true;
@@ -582,7 +630,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       bool handed_back = false, handed_back_late = false;
       if constexpr (OUT_BYTES == 2) {
         if (p.acc_slots == 1 && staged && tile_n == 256 && !contributes && !finishes && !scale_out && !bias && !out_f16 &&
-            row0 < rows_m) {
+            !p.out_quant && row0 < rows_m) {
           auto pack64 = [](const uint32_t* f, uint32_t* w) {
 #pragma unroll
             for (int u = 0; u < 32; ++u)
@@ -693,6 +741,64 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
             const float mine = __ldg(bias + min(row, rows_m - 1));
 #pragma unroll
             for (int j = 0; j < CHUNK; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + mine);
+          }
+        }
+        if constexpr (OUT_BYTES == 2) {
+          if (p.out_quant && !contributes) {
+            // Block-scaled C: this thread quantises its row's 64 columns - four
+            // nvfp4 blocks or two mx blocks - from the accumulator rounded to
+            // bfloat16 (so the bytes equal those of quantising a bfloat16 C), and
+            // stores the packed codes and its scale bytes in the blocked layout.
+            if (row < rows_m) {
+              float x[64];
+#pragma unroll
+              for (int u = 0; u < 32; ++u) {
+                const uint32_t both = pack_bf16x2(__uint_as_float(v[2 * u]), __uint_as_float(v[2 * u + 1]));
+                x[2 * u] = __uint_as_float(both << 16);
+                x[2 * u + 1] = __uint_as_float(both & 0xFFFF0000u);
+              }
+              const int gc = col0 + c;
+              uint8_t* const atom_row = p.out_scales + (size_t(row >> 7) * p.out_k_groups) * 512 +
+                                        (row & 31) * 16 + ((row >> 5) & 3) * 4;
+              if (p.out_quant == 1 + Q_NVFP4) {
+                uint32_t words[8], scales = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                  uint32_t stored;
+                  quantize_block<Q_NVFP4>(x + 16 * b, words + 2 * b, stored);
+                  scales |= (stored & 0xFFu) << (8 * b);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(out + size_t(row) * (rows_n >> 1) + (gc >> 1));
+                dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+                dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+                *reinterpret_cast<uint32_t*>(atom_row + size_t(gc >> 6) * 512) = scales;
+              } else if (p.out_quant == 1 + Q_MXFP4) {
+                uint32_t words[8], scales = 0;
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                  uint32_t stored;
+                  quantize_block<Q_MXFP4>(x + 32 * b, words + 4 * b, stored);
+                  scales |= (stored & 0xFFu) << (8 * b);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(out + size_t(row) * (rows_n >> 1) + (gc >> 1));
+                dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+                dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+                *reinterpret_cast<uint16_t*>(atom_row + size_t(gc >> 7) * 512 + ((gc >> 5) & 3)) = uint16_t(scales);
+              } else {
+                uint32_t words[16], scales = 0;
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                  uint32_t stored;
+                  quantize_block<Q_MXFP8>(x + 32 * b, words + 8 * b, stored);
+                  scales |= (stored & 0xFFu) << (8 * b);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(out + size_t(row) * rows_n + gc);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) dst[u] = make_uint4(words[4 * u], words[4 * u + 1], words[4 * u + 2], words[4 * u + 3]);
+                *reinterpret_cast<uint16_t*>(atom_row + size_t(gc >> 7) * 512 + ((gc >> 5) & 3)) = uint16_t(scales);
+              }
+            }
+            continue;
           }
         }
         if (contributes) {

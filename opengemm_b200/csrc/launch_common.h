@@ -122,6 +122,9 @@ struct LaunchPointers {
   const void* sfb;
   void* c;
   const void* bias;  // float32 [n], added to every row of C before it is stored; may be null
+  // Block-scaled output: `c` receives packed codes, `c_scales` the blocked scales.
+  int out_quant = 0;        // 0 off, else 1 nvfp4, 2 mxfp8, 3 mxfp4
+  void* c_scales = nullptr;
 };
 
 // Checks every launch entry point makes before touching the device.
@@ -138,6 +141,21 @@ inline int check_pointers(const OgGemm& g, const Plan& p, const LaunchPointers& 
   if (p.format->scaled && (!io.sfa || !io.sfb)) {
     snprintf(why, why_cap, "a block-scaled format takes both sfa and sfb");
     return OG_ERR_LAUNCH;
+  }
+  if (io.out_quant) {
+    if (!io.c_scales) {
+      snprintf(why, why_cap, "a block-scaled output takes a scale buffer");
+      return OG_ERR_LAUNCH;
+    }
+    if (p.format->out != OUT_BF16) {
+      snprintf(why, why_cap, "dtype %.16s writes no bfloat16: bind a block-scaled format or \"<format>.bf16\" to quantise C", g.dtype);
+      return OG_ERR_LAUNCH;
+    }
+    if (p.swap || p.tile_n % 64 || g.n % 64) {
+      snprintf(why, why_cap, "a block-scaled output needs N %% 64 == 0, tiles a multiple of 64 wide and no operand swap "
+               "(n = %d, tile width %d, swap_ab = %d)", g.n, p.tile_n, p.swap);
+      return OG_ERR_LAUNCH;
+    }
   }
   if ((alpha || io.bias) && p.format->out == OUT_S32) {
     snprintf(why, why_cap, "dtype %.16s accumulates integers exactly: its output cannot be scaled or biased", g.dtype);
@@ -225,6 +243,11 @@ inline int fill_params(const Plan& p, const OgGemm& g, const LaunchPointers& io,
   if (alpha) {
     params.scale_out = 1;
     params.alpha = *alpha;
+  }
+  if (io.out_quant) {
+    params.out_quant = io.out_quant;
+    params.out_scales = static_cast<uint8_t*>(io.c_scales);
+    params.out_k_groups = ceil_div(g.n, io.out_quant == 1 ? 64 : 128);
   }
   return OG_OK;
 }

@@ -130,6 +130,8 @@ struct Plan {
   uint32_t idesc = 0;
   int acc_slots = 2, acc_stride = 0, sf_col = 0, sf_slots = 1, sf_cols = 0, tmem_cols = 32;
   int epi_staged = 0, epi_tma = 0, out_bytes = 4;
+  int epi = 0;        // 0 each thread stores its own row, 1 rows staged in shared memory, 2 staged and stored by TMA
+  int smem_bits = 8;  // bits per value in shared memory
   int sf_atoms = 0, sf_yblocks = 0, k_groups = 0;
   int smem_bytes = 0;
   int x_bits = 0, y_bits = 0;        // global bits per value of the X / Y operand
@@ -148,6 +150,54 @@ inline int pow2_at_least(int x) {
   int p = 32;
   while (p < x) p *= 2;
   return p;
+}
+
+// The part of a tile plan that does not depend on the problem's extents: what
+// follows from the MMA kind, the pair size, the output width, the tile width
+// and the epilogue path alone.  make_plan derives these fields here, and the
+// kernels that are compiled for one such plan (kernels_fixed.cu) fold the same
+// values in at compile time, so the two cannot drift apart.
+struct TileShape {
+  int tile_n = 0, block_k = 0, mma_k = 0;
+  int x_bytes = 0, y_bytes = 0, sf_bytes = 0, stage_bytes = 0;
+  int sf_atoms = 0, sf_yblocks = 0, sf_cols = 0;
+  int epi_staged = 0, epi_tma = 0, stages = 0;
+  int acc_slots = 0, acc_stride = 0, sf_col = 0, sf_slots = 0, tmem_cols = 0;
+  int smem_bytes = 0;
+};
+
+// `smem_bits`: bits per value in shared memory (16 f16/bf16, 32 tf32, 8 for
+// every 8-bit container, 4 for packed fp4); `sf_block`: values per scale, 0
+// for a dense kind; `epi`: 0 each thread stores its own row, 1 rows staged in
+// shared memory, 2 staged and stored by TMA.
+constexpr TileShape tile_shape(int smem_bits, int sf_block, int cta_group, int out_bytes, int tile_n, int epi) {
+  TileShape t;
+  t.tile_n = tile_n;
+  t.block_k = 1024 / smem_bits;
+  t.mma_k = t.block_k / 4;
+  t.x_bytes = 128 * 128;
+  t.y_bytes = tile_n / cta_group * 128;
+  if (sf_block > 0) {
+    t.sf_atoms = t.block_k / (4 * sf_block);
+    t.sf_yblocks = tile_n > 128 ? 2 : 1;
+    t.sf_bytes = t.sf_atoms * 512 * (1 + t.sf_yblocks);
+    t.sf_cols = 4 * t.sf_atoms * (1 + t.sf_yblocks);
+  }
+  t.stage_bytes = (t.x_bytes + t.y_bytes + t.sf_bytes + 1023) / 1024 * 1024;
+  t.epi_staged = epi >= 1 ? 1 : 0;
+  t.epi_tma = (epi == 2 && out_bytes == 4) ? 1 : 0;
+  const int epi_bytes = t.epi_staged ? 4 * (t.epi_tma ? 2 : 1) * (32 * 128) : 0;
+  const int fit = (227 * 1024 - (1024 + 512) - epi_bytes) / t.stage_bytes;
+  t.stages = fit < 16 ? fit : 16;
+  t.smem_bytes = t.stages * t.stage_bytes + epi_bytes + 1024;
+  t.acc_stride = tile_n;
+  t.acc_slots = (2 * tile_n + t.sf_cols <= 512) ? 2 : 1;
+  t.sf_col = t.acc_slots * t.acc_stride;
+  t.sf_slots = (t.sf_cols && t.sf_col + 2 * t.sf_cols <= 512) ? 2 : 1;
+  int cols = 32;
+  while (cols < t.sf_col + t.sf_slots * t.sf_cols) cols *= 2;
+  t.tmem_cols = cols;
+  return t;
 }
 
 // K granularity a format accepts: TMA addresses rows 16 bytes at a time, the
@@ -209,57 +259,58 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
   p.tile_n = legal_tile_n(*f, p.cta_group, g.output_n > 0 ? g.output_n : 128, p.rows_n);
   const bool packed4 = f->scaled && ea->value_bits == 4;
   const int smem_bits = packed4 ? 4 : ex->smem_bits;
-  p.block_k = 1024 / smem_bits;
-  p.mma_k = p.block_k / 4;
-  p.k_blocks = ceil_div(p.k, p.block_k);
+  p.out_bytes = (f->out == OUT_BF16 || f->out == OUT_F16) ? 2 : 4;
+  p.k_blocks = ceil_div(p.k, 1024 / smem_bits);
+  const int64_t ldd = g.n;              // C is [m, n] row-major whichever way the MMA runs
+  // 32-bit output behind a long K loop leaves by TMA store (two buffers per
+  // warp); everything else staged leaves by plain stores (one buffer).
+  const bool staged = !g.epi_direct && !p.swap && (ldd * p.out_bytes) % 16 == 0;
+  const bool by_tma = staged && p.out_bytes == 4 && p.k_blocks >= 8 && p.tile_n % 32 == 0;
+  p.epi = by_tma ? 2 : staged ? 1 : 0;
+  const TileShape t = tile_shape(smem_bits, f->scaled ? f->sf_block : 0, p.cta_group, p.out_bytes, p.tile_n, p.epi);
+  p.block_k = t.block_k;
+  p.mma_k = t.mma_k;
   p.x_bits = ex->value_bits;
   p.y_bits = ey->value_bits;
   p.x_map = packed4 ? MAP_16U4_ALIGN8B : ex->map_type;
   p.y_map = packed4 ? MAP_16U4_ALIGN8B : ey->map_type;
   const int y_rows = p.tile_n / p.cta_group;
-  p.x_bytes = 128 * 128;
-  p.y_bytes = y_rows * 128;
-  if (f->scaled) {
-    p.sf_atoms = p.block_k / (4 * f->sf_block);
-    p.sf_yblocks = p.tile_n > 128 ? 2 : 1;
-    p.k_groups = ceil_div(p.k, 4 * f->sf_block);
-    p.sf_bytes = p.sf_atoms * 512 * (1 + p.sf_yblocks);
-    p.sf_cols = 4 * p.sf_atoms * (1 + p.sf_yblocks);
-  }
-  p.stage_bytes = round_up(p.x_bytes + p.y_bytes + p.sf_bytes, 1024);
+  p.x_bytes = t.x_bytes;
+  p.y_bytes = t.y_bytes;
+  p.sf_atoms = t.sf_atoms;
+  p.sf_yblocks = t.sf_yblocks;
+  p.sf_bytes = t.sf_bytes;
+  p.sf_cols = t.sf_cols;
+  if (f->scaled) p.k_groups = ceil_div(p.k, 4 * f->sf_block);
+  p.stage_bytes = t.stage_bytes;
   // Bytes TMA credits per stage: the packed global size for expanding maps.
   const int x_tx = 128 * p.block_k * (packed4 ? 4 : p.x_bits) / 8;
   const int y_tx = y_rows * p.block_k * (packed4 ? 4 : p.y_bits) / 8;
   p.tx_bytes = p.cta_group * (x_tx + y_tx + p.sf_bytes);
 
-  p.out_bytes = (f->out == OUT_BF16 || f->out == OUT_F16) ? 2 : 4;
-  const int64_t ldd = g.n;              // C is [m, n] row-major whichever way the MMA runs
-  p.epi_staged = (!g.epi_direct && !p.swap && (ldd * p.out_bytes) % 16 == 0) ? 1 : 0;
+  p.epi_staged = t.epi_staged;
+  p.epi_tma = t.epi_tma;
   p.tiles_m = ceil_div(p.rows_m, p.tile_m);
   p.tiles_n = ceil_div(p.rows_n, p.tile_n);
   p.num_tiles = p.tiles_m * p.tiles_n;
-  // 32-bit output behind a long K loop leaves by TMA store (two buffers per
-  // warp); everything else staged leaves by plain stores (one buffer).
-  p.epi_tma = (p.epi_staged && p.out_bytes == 4 && p.k_blocks >= 8 && p.tile_n % 32 == 0) ? 1 : 0;
-  const int epi_bytes = p.epi_staged ? 4 * (p.epi_tma ? 2 : 1) * EPI_BUF_BYTES_HOST : 0;
-  const int fit = (SMEM_LIMIT - SMEM_RESERVE - epi_bytes) / p.stage_bytes;
-  p.stages = std::min(fit, PLAN_MAX_STAGES);
+  p.stages = t.stages;
   if (g.stages > 0) p.stages = std::min(p.stages, std::max(2, (int)g.stages));
   if (p.stages < 2) {
     snprintf(why, why_cap, "a %d-wide tile of %s leaves no room for a two-stage ring", p.tile_n, f->name);
     return OG_ERR_NO_KERNEL;
   }
-  p.smem_bytes = p.stages * p.stage_bytes + epi_bytes + 1024;
+  p.smem_bytes = t.smem_bytes - (t.stages - p.stages) * t.stage_bytes;
 
-  p.acc_stride = p.tile_n;
-  p.acc_slots = (2 * p.tile_n + p.sf_cols <= 512) ? 2 : 1;
-  p.sf_col = p.acc_slots * p.acc_stride;
-  p.sf_slots = (p.sf_cols && p.sf_col + 2 * p.sf_cols <= 512) ? 2 : 1;
-  p.tmem_cols = pow2_at_least(p.sf_col + p.sf_slots * p.sf_cols);
+  p.acc_stride = t.acc_stride;
+  p.acc_slots = t.acc_slots;
+  p.sf_col = t.sf_col;
+  p.sf_slots = t.sf_slots;
+  p.tmem_cols = t.tmem_cols;
   if (p.tmem_cols > 512) {
     snprintf(why, why_cap, "a %d-wide tile of %s does not fit tensor memory", p.tile_n, f->name);
     return OG_ERR_NO_KERNEL;
   }
+  p.smem_bits = smem_bits;
 
   p.walk = (g.walk >= 0 && g.walk <= 4) ? g.walk : 0;
   {

@@ -110,18 +110,9 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
 // One attempt: the hardware parks the thread until the phase completes or the
 // hint (nanoseconds) runs out, so a waiting role does not burn issue slots and
 // power spinning - on a power-capped part that is tensor-core clock.
-constexpr uint32_t WAIT_PARK_NS = 1000000;
+constexpr uint32_t WAIT_PARK_NS = 500000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
-#ifdef OG_EXP_NOHINT
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
@@ -129,7 +120,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(done)
       : "r"(bar), "r"(parity), "r"(WAIT_PARK_NS)
       : "memory");
-#endif
   return done != 0;
 }
 
@@ -152,16 +142,15 @@ struct WaitCtx {
 // is reported where it arose rather than where it was felt.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           int site) {
-#pragma unroll 1
-  for (int spin = 0; spin < 64; ++spin)
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
+  // Not there yet.  Every further attempt may park the thread for up to
+  // WAIT_PARK_NS, so the clock and the abort flag are looked at once per
+  // attempt: a limit of a few milliseconds is kept to within one parking time.
   const uint64_t start = global_timer_ns();
   const uint64_t limit = (site == SITE_EPI_ACC_FULL || site == SITE_MMA_ACC_EMPTY) ? 2 * ctx.limit_ns : ctx.limit_ns;
 #pragma unroll 1
   while (true) {
-#pragma unroll 1
-    for (int spin = 0; spin < 32; ++spin)
-      if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if (*ctx.abort_flag) return false;
     if (global_timer_ns() - start > limit) {
       *ctx.abort_flag = 1;

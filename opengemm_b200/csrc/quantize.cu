@@ -26,125 +26,14 @@
 #include <cuda_runtime.h>
 
 #include "../../include/opengemm_b200.h"
+#include "quant_math.cuh"
 
 namespace og {
 namespace {
 
-enum QFormat { Q_NVFP4 = 0, Q_MXFP8 = 1, Q_MXFP4 = 2 };
-
-// float -> e4m3fn code, nearest even; magnitudes that round past 448 give NaN
-// (0x7F) as torch's cast does.  The input is non-negative or signed; NaN -> 0x7F.
-__device__ __forceinline__ uint32_t to_e4m3(float x) {
-  const uint32_t bits = __float_as_uint(x);
-  const uint32_t sign = (bits >> 24) & 0x80u;
-  const float mag = fabsf(x);
-  if (!(mag < 464.0f)) {
-    // 464 itself is the tie between 448 (even mantissa) and the NaN slot: it rounds to 448.
-    return sign | ((mag == 464.0f) ? 0x7Eu : 0x7Fu);
-  }
-  uint32_t code;
-  if (mag < 0.015625f) {  // below 2^-6: subnormals, spacing 2^-9
-    code = uint32_t(__float2int_rn(mag * 512.0f));  // rn = nearest even; 8 becomes the first normal
-  } else {
-    const uint32_t m = __float_as_uint(mag);
-    // keep 3 mantissa bits: add half of the dropped field with the even tie rule
-    const uint32_t rounded = m + 0x7FFFFu + ((m >> 20) & 1u);
-    const int exponent = int(rounded >> 23) - 127 + 7;
-    code = (uint32_t(exponent) << 3) | ((rounded >> 20) & 7u);
-  }
-  return sign | code;
-}
-
-__device__ __forceinline__ float from_e4m3(uint32_t code) {
-  const uint32_t e = (code >> 3) & 15u, m = code & 7u;
-  const float mag = e ? __uint_as_float(((e + 120u) << 23) | (m << 20)) : float(m) * 0.001953125f;
-  return (code & 0x80u) ? -mag : mag;
-}
-
-// Nearest e2m1 code (sign-magnitude, values 0 .5 1 1.5 2 3 4 6), a tie to the
-// even code.  A value that rounds to zero is stored as +0, as the reference's
-// scan leaves it.
-__device__ __forceinline__ uint32_t to_e2m1(float x) {
-  const float a = fabsf(x);
-  if (!(a < 64.0f)) {
-    // Far outside the format (the block's scale underflowed): float32 can no
-    // longer tell the distances to the sixteen values apart, and the
-    // reference's scan - keep the first best, move to an even code only from
-    // an odd one on an exact tie - decides.  Repeat that scan literally.
-    const float values[16] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
-    uint32_t code = 0;
-    float best = fabsf(__fsub_rn(x, values[0]));
-#pragma unroll
-    for (uint32_t c = 1; c < 16; ++c) {
-      const float d = fabsf(__fsub_rn(x, values[c]));
-      if (d < best || (d == best && (c & 1) == 0 && (code & 1) == 1)) best = d, code = c;
-    }
-    return code;
-  }
-  uint32_t code = 0;
-  code += a > 0.25f;   // tie at .25 stays at code 0 (even)
-  code += a >= 0.75f;  // tie at .75 goes up to code 2 (even)
-  code += a > 1.25f;   // tie at 1.25 stays at code 2
-  code += a >= 1.75f;  // tie goes up to code 4
-  code += a > 2.5f;    // tie stays at code 4
-  code += a >= 3.5f;   // tie goes up to code 6
-  code += a > 5.0f;    // tie stays at code 6
-  return (code && x < 0.f) ? (code | 8u) : code;
-}
-
-// Eight float32 values -> eight e2m1 codes in one 32-bit word (value 0 in the
-// low nibble) with the hardware's packed conversion: nearest even, saturating
-// at +-6.  The hardware keeps the sign of a value that rounds to zero; the
-// reference stores +0 there, so sign bits of zero magnitudes are cleared.
-__device__ __forceinline__ uint32_t pack_e2m1x8(const float* q) {
-  uint32_t w = 0;
-#pragma unroll
-  for (int h = 0; h < 4; ++h) {
-    uint32_t byte;
-    asm("{\n\t.reg .b8 t;\n\t"
-        "cvt.rn.satfinite.e2m1x2.f32 t, %2, %1;\n\t"
-        "cvt.u32.u8 %0, t;\n\t}"
-        : "=r"(byte)
-        : "f"(q[2 * h]), "f"(q[2 * h + 1]));
-    w |= byte << (8 * h);
-  }
-  const uint32_t magnitude = w & 0x77777777u;
-  const uint32_t nonzero = ((magnitude + 0x77777777u) | magnitude) & 0x88888888u;
-  return magnitude | (w & nonzero);
-}
-
-// Four float32 values -> four e4m3 codes, nearest even (every quotient of a
-// block is at most 448 in magnitude, so saturation never differs from torch).
-__device__ __forceinline__ uint32_t pack_e4m3x4(const float* q) {
-  uint32_t lo, hi;
-  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}"
-      : "=r"(lo) : "f"(q[0]), "f"(q[1]));
-  asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}"
-      : "=r"(hi) : "f"(q[2]), "f"(q[3]));
-  return lo | (hi << 16);
-}
-
-__device__ __forceinline__ float through_bf16(float x) {
-  return __bfloat162float(__float2bfloat16_rn(x));
-}
-
 constexpr int Q_THREADS = 256;
 constexpr int Q_GROUPS = 8;                 // K groups (of four scale blocks) per CTA
 constexpr int Q_BLOCKS = Q_GROUPS * 4;      // scale blocks along K per CTA
-
-// x / s, correctly rounded, for a divisor that is a ue4m3 value (at most four
-// significant bits).  q0 = x * (1/s) is refined once with the exact residual;
-// the true quotient a / b (a < 2^24, b <= 15 after scaling) is either exactly
-// representable or at least 2^-30 (relative) away from every float32
-// rounding boundary, far more than the refined value's error, so the result
-// equals IEEE division.  Tiny numerators, whose quotient could be subnormal,
-// take the library division.
-__device__ __forceinline__ float divide_exact(float x, float s, float inverse) {
-  if (fabsf(x) < 1e-30f) return __fdiv_rn(x, s);
-  const float q0 = x * inverse;
-  const float residual = __fmaf_rn(-q0, s, x);
-  return __fmaf_rn(residual, inverse, q0);
-}
 
 // A CTA covers 128 rows x 32 scale blocks.  One thread quantises one scale
 // block at a time (16 or 32 values, 32-128 bytes of input); the 32 lanes of a
@@ -193,8 +82,25 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_kernel(const void* __restr
         }
       }
       float amax = 0.f;
+      if constexpr (F32_IN) {
 #pragma unroll
-      for (int i = 0; i < BLOCK; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        for (int i = 0; i < BLOCK; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      } else {
+        // bfloat16 input: the largest magnitude by packed pairs, two values per
+        // instruction; the comparison of magnitudes is exact in any width.
+        uint32_t m2 = absmax_bf16x2(raw[0].x, raw[0].y);
+        m2 = absmax_bf16x2(m2, absmax_bf16x2(raw[0].z, raw[0].w));
+#pragma unroll
+        for (int i = 1; i < LOADS; ++i) {
+          m2 = absmax_bf16x2(m2, absmax_bf16x2(raw[i].x, raw[i].y));
+          m2 = absmax_bf16x2(m2, absmax_bf16x2(raw[i].z, raw[i].w));
+        }
+        amax = fmaxf(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xFFFF0000u));
+        bool any_nan = false;  // max.bf16x2 drops NaN operands; the reference's amax keeps them
+#pragma unroll
+        for (int i = 0; i < BLOCK; ++i) any_nan |= (v[i] != v[i]);
+        if (any_nan) amax = __uint_as_float(0x7FC00000u);
+      }
       // amax / 6 and amax / 448 by the same exact reciprocal refinement (3 and 7
       // are the divisors' odd parts); tiny or huge amax takes the library division.
       constexpr float TOP_INVERSE = 1.0f / TOP;
@@ -223,13 +129,23 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_kernel(const void* __restr
       // A ue4m3 scale that underflowed to zero (divisor 1e-30) or overflowed to NaN
       // is rare: those blocks take the library division.
       const bool plain = FORMAT == Q_NVFP4 && ((stored & 0x7Fu) == 0x7Fu || (stored & 0x7Fu) == 0u);
+      // bfloat16 values over a ue4m3 divisor: numerator and divisor carry 8 and 4
+      // significant bits, so the exact quotient is either a bfloat16 value itself
+      // (the divisor's odd part divides the numerator) or a fraction whose binary
+      // expansion repeats with a period of at most 12 bits and therefore stays
+      // 2^-14 (relative) or more away from every bfloat16 rounding boundary.  The
+      // one-multiply estimate x * (1/s) is within 2^-23 of it: rounded to
+      // bfloat16 it gives the same value as the correctly rounded float32
+      // quotient does (and rounding that to float32 first changes nothing, for
+      // the same reason).
+      const bool short_quotient = FORMAT == Q_NVFP4 && !F32_IN && !plain;
       float q[BLOCK];
 #pragma unroll
       for (int i = 0; i < BLOCK; i += 2) {
         float pair[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          if (exact_inverse) pair[h] = v[i + h] * inverse;
+          if (exact_inverse || short_quotient) pair[h] = v[i + h] * inverse;
           else if (FORMAT != Q_NVFP4 || plain) pair[h] = __fdiv_rn(v[i + h], divisor);
           else pair[h] = divide_exact(v[i + h], divisor, inverse);
         }

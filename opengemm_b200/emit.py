@@ -190,6 +190,8 @@ def emit(name, m, n, k, config, stem):
         + "\n"
         + _strip((CSRC / "raster.h").read_text())
         + "\n"
+        + _strip((CSRC / "quant_math.cuh").read_text())
+        + "\n"
         + _strip((CSRC / "kernel.cuh").read_text())
     )
     values = dict(plan)

@@ -497,11 +497,15 @@ def check_f16_output(got_bits, want_f32):
     """Acceptance for a dense format whose f32 accumulator is rounded to IEEE
     half on the way out (an output variant this build adds): every output
     within one half unit in the last place of the float32 reference, plus
-    2^-20 of the largest |reference| (the same cancellation floor as
-    `check_bf16_output`).  Returns (ok, worst excess in ulps)."""
+    2^-16 of the largest |reference|.  The floor is the accumulation's own
+    error - the tensor cores' sums of K products differ from a float32 matmul
+    by a few 2^-20 of the largest output (more for tf32 operands), which a
+    half's 11-bit significand resolves where bfloat16's 8 bits do not; it
+    stays 64 times tighter than the 1e-3 bound on float32 output.
+    Returns (ok, worst excess in ulps)."""
     got = np.asarray(got_bits).view(np.float16).astype(np.float64)
     want = np.asarray(want_f32, dtype=np.float64)
-    floor = 2.0**-20 * (float(np.abs(want).max()) if want.size else 0.0)
+    floor = 2.0**-16 * (float(np.abs(want).max()) if want.size else 0.0)
     excess = (np.abs(got - want) - floor) / f16_ulp(want)
     bad = ~(excess <= 1.0)
     return (not bad.any()), float(np.nanmax(excess)) if excess.size else 0.0

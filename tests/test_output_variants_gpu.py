@@ -242,3 +242,72 @@ def test_bias_through_gemm_and_its_refusals():
     i8 = torch.ones((128, 128), device="cuda", dtype=torch.int8)
     with pytest.raises(TypeError):
         og.gemm(i8, i8, bias=torch.zeros(128, device="cuda"))
+
+
+@pytest.mark.parametrize("out_format", ["nvfp4", "mxfp8", "mxfp4"])
+@pytest.mark.parametrize("name,shape,knobs", [
+    ("nvfp4", (300, 512, 768), dict(use_2cta=False, output_n=128)),
+    ("nvfp4", (2304, 2560, 1024), dict(use_2cta=True, output_n=256)),   # single accumulator
+    ("mxfp8", (1000, 1024, 512), dict(use_2cta=True, output_n=192)),
+    ("e4m3", (77, 192, 256), dict(use_2cta=False, output_n=64)),        # a dense format through its bfloat16-output kernel
+    ("bf16", (2304, 2560, 1024), dict(use_2cta=True, output_n=128, split_k=2)),  # stream-K: quantised once, by the finisher
+], ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else None)
+def test_block_scaled_output_equals_quantising_the_bfloat16_product(name, shape, knobs, out_format):
+    """C written block-scaled by the epilogue (og_b200_launch_quantized) against
+    the same GEMM written as bfloat16 and then quantised by the oracle's
+    restatement of the reference's quantize + to_blocked: the same bytes."""
+    m, n, k = shape
+    case = make_case(name, m, n, k, seed=55)
+    base = og.dtypes.lookup(name)
+    scaled = base.impl == "smm"
+    kernel_name = name if scaled else name + ".bf16"
+    d = og.dtypes.lookup(kernel_name)
+    config = heuristic_config(name, m, n, k)
+    config.update(knobs, swap_ab=False, cluster_m=2 if knobs["use_2cta"] else 1)
+    lib, g = capi.bind(kernel_name, m, n, k, config)
+    a, b = to_device(case["a"], d.a), to_device(case["b"], d.b)
+    sfa = to_device(case["sfa"], d.sf) if scaled else None
+    sfb = to_device(case["sfb"], d.sf) if scaled else None
+    plain = torch.empty((m, n), device="cuda", dtype=torch.bfloat16)
+    lib.launch(g, a, b, sfa, sfb, plain)
+    target = og.DTYPES[out_format]
+    packed = torch.full((m, n // 2 if target.bits == 4 else n), 0x7B, device="cuda", dtype=torch.uint8)
+    block = 16 if out_format == "nvfp4" else 32
+    scale_bytes = (-(-m // 128) * 128) * (-(-(n // block) // 4) * 4)
+    scales = torch.zeros(scale_bytes, device="cuda", dtype=torch.uint8)
+    lib.launch_quantized(g, a, b, sfa, sfb, packed, scales, out_format)
+    torch.cuda.synchronize()
+    c = ora.bf16_to_f32(plain.view(torch.int16).cpu().numpy().view(np.uint16))
+    want_packed, want_scales = ora.quantize(c, out_format)
+    assert np.array_equal(packed.cpu().numpy(), np.asarray(want_packed).view(np.uint8).reshape(m, -1))
+    assert np.array_equal(scales.cpu().numpy(), ora.to_blocked(want_scales))
+
+
+def test_block_scaled_output_through_gemm_feeds_the_next_gemm():
+    """gemm(..., out_format=) hands back operands the next block-scaled gemm() takes as they are."""
+    m, n, k, n2 = 256, 512, 1024, 384
+    first = make_case("nvfp4", m, n, k, seed=61)
+    second = make_case("nvfp4", n2, n2, n, seed=62)  # only its B operand (n2 x n) is used
+    d = og.DTYPES["nvfp4"]
+    a, b = to_device(first["a"], d.a), to_device(first["b"], d.b)
+    sfa, sfb = to_device(first["sfa"], d.sf), to_device(first["sfb"], d.sf)
+    packed, scales = og.gemm(a, b, sfa, sfb, out_format="nvfp4")
+    assert packed.dtype is d.a and packed.shape == (m, n // 2) and scales.dtype is d.sf
+    b2, sfb2 = to_device(second["b"], d.b), to_device(second["sfb"], d.sf)
+    chained = og.gemm(packed, b2, scales, sfb2)
+    torch.cuda.synchronize()
+    # the oracle's view of the chain: quantise the oracle-checked bfloat16 C, then the second product
+    c = og.gemm(a, b, sfa, sfb)
+    torch.cuda.synchronize()
+    qc, qs = ora.quantize(ora.bf16_to_f32(c.view(torch.int16).cpu().numpy().view(np.uint16)), "nvfp4")
+    want = ora.reference("nvfp4", np.asarray(qc).view(np.uint8).reshape(m, -1), second["b"], qs, second["sfb_raw"])
+    got = chained.view(torch.int16).cpu().numpy().view(np.uint16)
+    ok, worst = ora.check_close("nvfp4", n, got, want)
+    assert ok, worst
+    ok, figure = ora.check_north_star("nvfp4", got, want)
+    assert ok, figure
+    with pytest.raises(ValueError, match="multiple of 64"):
+        og.gemm(a, to_device(first["b"][:200], d.b), sfa, sfb, out_format="nvfp4")
+    i8 = torch.ones((128, 128), device="cuda", dtype=torch.int8)
+    with pytest.raises(TypeError):
+        og.gemm(i8, i8, out_format="mxfp8")
