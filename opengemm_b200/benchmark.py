@@ -12,10 +12,12 @@ Counterpart of the reference's suite runner (scripts/benchmark.py:1-60): the
 same harness on both sides (rotating operand sets larger than twice L2, CUDA
 events around back-to-back launches, medians of windows), a JSON report, and a
 non-zero exit status if any result is incorrect or fails to launch, so the run
-doubles as a regression test.  Two differences: a shape with no stored entry is
+doubles as a regression test.  One difference: a shape with no stored entry is
 measured with the heuristic configuration `gemm()` falls back to (and marked
-`heuristic`) instead of being skipped, and formats torch has no kernel for
-report no baseline (no CUTLASS comparator is wired in).
+`heuristic`) instead of being skipped.  Formats torch has no kernel for (u8,
+e5m2, e3m2, e2m3, e2m1, mxfp4) are compared, as in the reference
+(scripts/benchmark.py:90-119), with the fastest correct configuration of the
+CUTLASS stand-in library when `--cutlass DIR` (default oracle/_ref) holds one.
 """
 
 import argparse
@@ -35,7 +37,36 @@ from .log import log
 LOW_SPEEDUP = 0.95
 
 
-def measure(name, m, n, k, window_ms, tune_missing=False):
+def cutlass_baseline(directory, buffers, name, m, n, k, window_ms):
+    """The fastest CUTLASS configuration that reproduces the reference product:
+    `(callable, tile label)`, or `(None, reason)`.  Every configuration is
+    checked before it is timed, so a baseline that computes the wrong thing
+    cannot flatter the kernel compared with it."""
+    from . import compare
+
+    if directory is None or compare.cutlass_baselines(directory) is None:
+        return None, "no CUTLASS comparator built"
+    want = harness.reference(buffers[0], name)
+    rtol, atol = harness.tolerance(name, k)
+    best, wrong = None, []
+    checks = dict(compare.cutlass_runners(directory, name, m, n, k, buffers[:1]))
+    for tile, call in compare.cutlass_runners(directory, name, m, n, k, buffers):
+        try:
+            out = checks[tile]()
+            torch.cuda.synchronize()
+            torch.testing.assert_close(out, want, rtol=rtol, atol=atol)
+            us = harness.timed(call, window_ms=min(window_ms, 20.0), repeats=1)
+        except Exception as exc:
+            wrong.append(f"{tile}: {str(exc).splitlines()[0][:60]}")
+            continue
+        if best is None or us < best[0]:
+            best = (us, call, tile)
+    if best is None:
+        return None, ("no CUTLASS configuration for this format" if not wrong else "no CUTLASS tile worked: " + "; ".join(wrong))
+    return best[1], best[2]
+
+
+def measure(name, m, n, k, window_ms, tune_missing=False, cutlass=None):
     """One row of the report."""
     row = {"dtype": name, "m": m, "n": n, "k": k}
     stored = configs.stored_entry(name, m, n, k)
@@ -62,6 +93,13 @@ def measure(name, m, n, k, window_ms, tune_missing=False):
         return row
     kernel = harness.runner(buffers, bound)
     baseline, why = harness.baseline_for(buffers, name)
+    baseline_kind = "library"
+    if baseline is None:
+        baseline, tile_or_why = cutlass_baseline(cutlass, buffers, name, m, n, k, window_ms)
+        if baseline is not None:
+            baseline_kind = f"cutlass {tile_or_why}"
+        elif cutlass is not None:
+            why = f"{why}; {tile_or_why}"
     # Windows of the two sides alternate, so that clock and temperature drift
     # on a power-capped GPU falls on both alike; medians of three each.
     ours, theirs = [], []
@@ -77,7 +115,7 @@ def measure(name, m, n, k, window_ms, tune_missing=False):
                tile=f"{plan['tile_m']}x{plan['tile_n']}")
     if baseline:
         base = statistics.median(theirs)
-        row.update(baseline_us=round(base, 3), speedup=round(base / us, 3))
+        row.update(baseline_us=round(base, 3), speedup=round(base / us, 3), baseline_kind=baseline_kind)
     else:
         row["baseline"] = why
     return row
@@ -107,6 +145,8 @@ def main(argv=None):
     ap.add_argument("--shape", nargs=3, type=int, metavar=("M", "N", "K"))
     ap.add_argument("--quick", action="store_true", help="10 ms timing windows instead of 100 ms")
     ap.add_argument("--tune-missing", action="store_true")
+    ap.add_argument("--cutlass", default=str(Path(__file__).resolve().parents[1] / "oracle" / "_ref"),
+                    help="folder holding libcutlass_ref.so, the CUTLASS stand-in baselines (skipped when absent)")
     ap.add_argument("--output", default=None, help="JSON report (default results/perf_<gpu>_<date>.json)")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
@@ -118,7 +158,7 @@ def main(argv=None):
     for name in args.dtype:
         for m, n, k in shapes:
             try:
-                row = measure(name, m, n, k, window_ms, args.tune_missing)
+                row = measure(name, m, n, k, window_ms, args.tune_missing, cutlass=args.cutlass)
             except Exception as exc:  # a failed launch is a result, not the end of the sweep
                 row = {"dtype": name, "m": m, "n": n, "k": k, "status": f"FAILED: {str(exc).splitlines()[0][:120]}"}
             rows.append(row)

@@ -315,8 +315,13 @@ class Library:
             raise RuntimeError(self._quantize_error().decode())
 
     def set_independent_inputs(self, yes):
-        """Vouch (or stop vouching) that no earlier kernel of the stream writes a launch's operands."""
+        """Vouch (or stop vouching) that no earlier kernel of the stream writes a launch's
+        operands.  Process-wide; returns the previous setting, so a tool that turns it on
+        for its own loop can put it back."""
+        global _independent_inputs
+        before, _independent_inputs = _independent_inputs, bool(yes)
         self._independent(int(bool(yes)))
+        return before
 
     def set_fixed_kernels(self, yes):
         """Let launches use the kernels compiled for one tile shape (default), or send all to the run-time kernel."""
@@ -327,6 +332,7 @@ class Library:
 
 
 _libraries, _lock = {}, threading.Lock()
+_independent_inputs = False  # mirror of the library's process-wide switch
 
 
 def library(impl):

@@ -119,6 +119,81 @@ def interleaved(found, name, m, n, k, sets, ours=None, windows=4, window_ms=60.0
     }
 
 
+# ---- CUTLASS stand-in baselines -------------------------------------------------
+#
+# For the formats torch has no library kernel for (u8, e5m2, e3m2, e2m3, e2m1,
+# mxfp4) the reference's scripts fall back on CUTLASS GEMMs compiled into a small
+# library with a C ABI of its own (scripts/utils/cutlass_ref.py:31,54-73,
+# scripts/utils/cutlass_ref.cu: ogref_abi / ogref_configs / ogref_config_dtype /
+# ogref_config_tile / ogref_launch).  oracle/build_reference_kernels.py --cutlass
+# builds that library; this is the wiring that lets the suite runner use it as
+# the second baseline.  A comparator only: never loaded by the product path.
+
+CUTLASS_ABI = 1
+_cutlass = {}
+
+
+class CutlassBaselines:
+    """`libcutlass_ref.so` through its six `ogref_*` entry points."""
+
+    def __init__(self, path):
+        import ctypes
+        from ctypes import c_char_p, c_int32, c_void_p
+
+        lib = ctypes.CDLL(str(path))
+        lib.ogref_abi.restype = c_int32
+        lib.ogref_error.restype = c_char_p
+        lib.ogref_configs.restype = c_int32
+        lib.ogref_config_dtype.restype, lib.ogref_config_dtype.argtypes = c_char_p, [c_int32]
+        lib.ogref_config_tile.restype, lib.ogref_config_tile.argtypes = c_char_p, [c_int32]
+        lib.ogref_launch.restype = c_int32
+        lib.ogref_launch.argtypes = [c_int32] * 4 + [c_void_p] * 6
+        if lib.ogref_abi() != CUTLASS_ABI:
+            raise RuntimeError(f"{path} speaks comparator ABI {lib.ogref_abi()}, expected {CUTLASS_ABI}")
+        self._lib = lib
+
+    def configs(self, name):
+        """`(index, tile label)` of every configuration compiled for format `name`."""
+        return [(i, self._lib.ogref_config_tile(i).decode()) for i in range(self._lib.ogref_configs())
+                if self._lib.ogref_config_dtype(i).decode() == name]
+
+    def launch(self, index, m, n, k, a, b, sfa, sfb, out):
+        status = self._lib.ogref_launch(
+            index, m, n, k, a.data_ptr(), b.data_ptr(), 0 if sfa is None else sfa.data_ptr(),
+            0 if sfb is None else sfb.data_ptr(), out.data_ptr(), capi.raw_stream(a.get_device()))
+        if status != 0:
+            raise RuntimeError(self._lib.ogref_error().decode())
+
+
+def cutlass_baselines(directory):
+    """The CUTLASS comparator under `directory`, or None when it was not built."""
+    path = Path(directory) / "libcutlass_ref.so"
+    if not path.exists():
+        return None
+    if str(path) not in _cutlass:
+        _cutlass[str(path)] = CutlassBaselines(path)
+    return _cutlass[str(path)]
+
+
+def cutlass_runners(directory, name, m, n, k, buffers):
+    """`(tile label, callable)` for every CUTLASS configuration of `name` over the
+    rotating `buffers` (harness.Inputs); each call returns the output it wrote."""
+    library = cutlass_baselines(directory)
+    if library is None:
+        return []
+    out = []
+    for index, tile in library.configs(name):
+        cycle = itertools.cycle(buffers)
+
+        def call(index=index, cycle=cycle):
+            r = next(cycle)
+            library.launch(index, m, n, k, r.a, r.b, r.sfa, r.sfb, r.out)
+            return r.out
+
+        out.append((tile, call))
+    return out
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--dir", required=True, help="folder with the other build's two libraries and reference_configs.json")
@@ -131,7 +206,7 @@ def main():
     found = reference_libraries(args.dir)
     if found is None:
         raise SystemExit(f"{args.dir} does not hold libopengemm_mm.so, libopengemm_smm.so and reference_configs.json")
-    capi.library(DTYPES[args.dtype].impl).set_independent_inputs(True)  # the other library overlaps consecutive launches too
+    capi.library(DTYPES[args.dtype].impl).set_independent_inputs(True)  # the other library overlaps consecutive launches too (this process ends after the comparison)
     for m, n, k in args.shape:
         buffers = harness.make_input_set(m, n, k, args.dtype, cap_bytes=6 << 30)
         sets = [(r.a, r.b, r.sfa, r.sfb, r.out) for r in buffers]

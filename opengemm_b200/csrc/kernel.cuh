@@ -667,7 +667,33 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         }
       }
 
-      for (int c = 0; !handed_back && c < tile_n && col0 + c < rows_n; c += CHUNK) {
+      // A finisher first makes sure every sharer's partial sums are published,
+      // then keeps the loads of the first sharer's next chunk in flight while
+      // it works on the current one (32-bit output; two sharers is the common
+      // cut), so the tile costs one L2 round trip rather than one per chunk.
+      constexpr bool AHEAD = OUT_BYTES == 4;
+      int first_sharer = 0;
+      bool sharers_ready = true;
+      if (finishes) {
+        last_sharer = work.last_sharer(w);
+        for (int j = cluster_id + 1; j <= last_sharer && sharers_ready; ++j)
+          if (work.has_work(j)) {
+            if (!first_sharer) first_sharer = j;
+            sharers_ready = wait_flag(p.flags + my_region + (j - cluster_id) * CTA_GROUP * 4, p.epoch, ctx);
+          }
+      }
+      auto partial_of = [&](int j, int c) {
+        return reinterpret_cast<const uint4*>(p.partial) +
+               (size_t(my_region + (j - cluster_id) * CTA_GROUP * 4) * 64 + (c >> 2)) * 32 + lane;
+      };
+      uint4 ahead[AHEAD ? CHUNK / 4 : 1];
+      if (AHEAD && finishes && sharers_ready && first_sharer) {
+        const uint4* src = partial_of(first_sharer, 0);
+#pragma unroll
+        for (int u = 0; u < CHUNK / 4; ++u) ahead[AHEAD ? u : 0] = (4 * u < tile_n) ? __ldcg(src + u * 32) : make_uint4(0u, 0u, 0u, 0u);
+      }
+
+      for (int c = 0; !handed_back && sharers_ready && c < tile_n && col0 + c < rows_n; c += CHUNK) {
         const int width = min(CHUNK, tile_n - c);
         uint32_t v[CHUNK];
         if (width >= 32) tmem_ld_32(acc_tmem + c, v);
@@ -692,25 +718,26 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         }
 
         if (finishes) {
-          // Partial sums of every cluster that shares this tile.  All loads of
-          // a chunk are requested before any is used, so the L2 round trips
-          // overlap instead of queueing behind one another.
-          if (c == 0) {
-            last_sharer = work.last_sharer(w);
-            bool all_here = true;
-            for (int j = cluster_id + 1; j <= last_sharer && all_here; ++j)
-              if (work.has_work(j))
-                all_here = wait_flag(p.flags + my_region + (j - cluster_id) * CTA_GROUP * 4, p.epoch, ctx);
-            if (!all_here) break;
-          }
+          // Partial sums of every cluster that shares this tile.
           for (int j = cluster_id + 1; j <= last_sharer; ++j) {
             if (!work.has_work(j)) continue;
-            const uint4* src = reinterpret_cast<const uint4*>(p.partial) +
-                               (size_t(my_region + (j - cluster_id) * CTA_GROUP * 4) * 64 + (c >> 2)) * 32 + lane;
             uint4 q[CHUNK / 4];
+            if (AHEAD && j == first_sharer) {
 #pragma unroll
-            for (int u = 0; u < CHUNK / 4; ++u)
-              q[u] = (4 * u < width) ? __ldcg(src + u * 32) : make_uint4(0u, 0u, 0u, 0u);
+              for (int u = 0; u < CHUNK / 4; ++u) q[u] = ahead[AHEAD ? u : 0];
+              const int next = c + CHUNK;
+              if (next < tile_n && col0 + next < rows_n) {  // the next chunk's loads go out before this one's sums are used
+                const uint4* src = partial_of(j, next);
+#pragma unroll
+                for (int u = 0; u < CHUNK / 4; ++u)
+                  ahead[AHEAD ? u : 0] = (4 * u < tile_n - next) ? __ldcg(src + u * 32) : make_uint4(0u, 0u, 0u, 0u);
+              }
+            } else {
+              const uint4* src = partial_of(j, c);
+#pragma unroll
+              for (int u = 0; u < CHUNK / 4; ++u)
+                q[u] = (4 * u < width) ? __ldcg(src + u * 32) : make_uint4(0u, 0u, 0u, 0u);
+            }
             if (p.acc_int) {
 #pragma unroll
               for (int u = 0; u < CHUNK / 4; ++u)

@@ -112,7 +112,15 @@ def tune(name, m, n, k, verbose=False, window_ms=15.0, final_ms=60.0):
     """
     impl = DTYPES[name].impl
     library = capi.library(impl)
-    library.set_independent_inputs(True)  # the operand sets below are written once, before any launch
+    # the operand sets below are written once, before any launch; the caller's setting comes back at the end
+    independent_before = library.set_independent_inputs(True)
+    try:
+        return _tune(name, m, n, k, impl, library, verbose, window_ms, final_ms)
+    finally:
+        library.set_independent_inputs(independent_before)
+
+
+def _tune(name, m, n, k, impl, library, verbose, window_ms, final_ms):
     buffers = harness.make_input_set(m, n, k, name)
     want = harness.reference(buffers[0], name)
     space = geometry_candidates(name, m, n, k)

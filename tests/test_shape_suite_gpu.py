@@ -9,6 +9,7 @@ import numpy as np
 import pytest
 import torch
 
+import bench
 from opengemm_b200 import capi, configs, harness
 from opengemm_b200.dtypes import DTYPES
 from oracle import opengemm_oracle as ora
@@ -21,30 +22,6 @@ CASES = [(NAMES[(3 * i + j) % len(NAMES)], shape) for i, shape in enumerate(SHAP
 # the two large shapes of the reference's own test list (scripts/test.py:23-30), for every format
 for _shape in [(2048, 2048, 2048), (1, 8192, 8192)]:
     CASES += [(name, _shape) for name in NAMES if (name, _shape) not in CASES]
-SAMPLE = 40
-
-
-def sample_indices(extent, rng):
-    """Up to SAMPLE indices: both ends, both sides of every 128 / 256 seam near
-    the ends and the middle, the rest random."""
-    seams = [0, extent - 1]
-    for at in (128, 192, 256, extent // 2 // 128 * 128, (extent - 1) // 256 * 256):
-        seams += [at - 1, at]
-    picks = [i for i in dict.fromkeys(seams) if 0 <= i < extent]
-    spare = SAMPLE - len(picks)
-    if spare > 0 and extent > len(picks):
-        picks += list(rng.choice(extent, size=min(spare, extent), replace=False))
-    return np.array(sorted(set(int(i) for i in picks))[:SAMPLE])
-
-
-def raw_rows(t, rows):
-    """Selected rows of a device tensor as the storage-typed numpy array the oracle reads."""
-    index = torch.from_numpy(rows).to(t.device)
-    if t.dtype in (torch.float32, torch.int8, torch.uint8):
-        return t[index].cpu().numpy()
-    if t.dtype in (torch.bfloat16, torch.float16):
-        return t.view(torch.int16)[index].cpu().numpy().view(np.uint16)
-    return t.view(torch.uint8)[index].cpu().numpy()  # fp8 codes, packed fp4 pairs
 
 
 @pytest.mark.parametrize("name,shape", CASES, ids=[f"{n}-{'x'.join(map(str, s))}" for n, s in CASES])
@@ -66,11 +43,12 @@ def test_suite_shape_matches_the_oracle_on_sampled_rows_and_columns(name, shape)
     assert int(status.item()) == 0, f"device wait gave up: {int(status.item())} ({lib.plan(g)})"
 
     rng = np.random.default_rng(m * 31 + n * 17 + k)
-    rows, cols = sample_indices(m, rng), sample_indices(n, rng)
+    rows, cols = bench.sample_indices(m, rng), bench.sample_indices(n, rng)
+    raw_rows = lambda t, index: bench.raw_rows(torch, t, index)
     sfa = raw_rows(inputs.sfa_raw, rows) if d.impl == "smm" else None
     sfb = raw_rows(inputs.sfb_raw, cols) if d.impl == "smm" else None
     want = ora.reference(name, raw_rows(inputs.a, rows), raw_rows(inputs.b, cols), sfa, sfb)
-    picked = out[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()].contiguous()
+    picked = out[torch.as_tensor(rows).cuda()][:, torch.as_tensor(cols).cuda()].contiguous()
     got = picked.view(torch.int16).cpu().numpy().view(np.uint16) if d.out is torch.bfloat16 else picked.cpu().numpy()
     ok, worst = ora.check_close(name, k, got, want)
     assert ok, f"{name} {m}x{n}x{k}: outside the reference tolerance by {worst}"
