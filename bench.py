@@ -859,10 +859,13 @@ def run_ours(args):
     except Exception as exc:
         roofline["cublas_same_shape"] = None
         roofline["cublas_note"] = str(exc)[:100]
-    try:
-        roofline["reference_kernel_same_shape"] = reference_kernel_leg(torch, r, unit)
-    except Exception as exc:
-        roofline["reference_kernel_same_shape"] = {"unavailable": str(exc)[:160]}
+    if args.no_side:
+        roofline["reference_kernel_same_shape"] = {"unavailable": "side measurements were switched off (--no-side)"}
+    else:
+        try:
+            roofline["reference_kernel_same_shape"] = reference_kernel_leg(torch, r, unit)
+        except Exception as exc:
+            roofline["reference_kernel_same_shape"] = {"unavailable": str(exc)[:160]}
 
     cpu = None
     if world == 1:

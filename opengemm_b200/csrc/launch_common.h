@@ -60,8 +60,16 @@ struct MapSlot {
   bool used = false;
 };
 
-constexpr int MAP_SLOTS = 256;
-inline thread_local MapSlot map_cache[MAP_SLOTS];
+// 64 sets of four ways: a loop over a few rotating operand sets keeps a dozen
+// or two maps alive, and in a direct-mapped table two of those would often
+// share a slot and evict each other on every call (a driver call each time).
+constexpr int MAP_SETS = 64;
+constexpr int MAP_WAYS = 4;
+struct MapSet {
+  MapSlot way[MAP_WAYS];
+  unsigned next = 0;  // the way the next miss replaces
+};
+inline thread_local MapSet map_cache[MAP_SETS];
 
 inline uint64_t mix_hash(uint64_t h, uint64_t v) {
   h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
@@ -79,11 +87,13 @@ inline int encode_2d(CUtensorMap* out, const void* base, int type, uint64_t dim0
   h = mix_hash(h, dim0 * 1315423911ull + dim1);
   h = mix_hash(h, (uint64_t(box0) << 32) | box1);
   h = mix_hash(h, stride * 31 + uint64_t(type) * 7 + uint64_t(swizzle) * 3 + uint64_t(l2));
-  MapSlot& slot = map_cache[h % MAP_SLOTS];
-  if (slot.used && slot.key == key) {
-    *out = slot.map;
-    return OG_OK;
-  }
+  MapSet& set = map_cache[h % MAP_SETS];
+  for (MapSlot& candidate : set.way)
+    if (candidate.used && candidate.key == key) {
+      *out = candidate.map;
+      return OG_OK;
+    }
+  MapSlot& slot = set.way[set.next++ % MAP_WAYS];
   EncodeFn encode = tensor_map_encoder();
   if (!encode) {
     snprintf(why, why_cap, "cuTensorMapEncodeTiled is not available: no CUDA driver");
