@@ -65,11 +65,9 @@ NOMINAL_BF16_TFLOPS = 2250.0
 # benchmark's own rotation of buffers, from the ncu captures summarised under
 # profiles/, keyed by (format, m, n, k); None where no capture is committed.
 NCU_TRAFFIC_BYTES = {
-    ("e4m3", 4096, 4096, 4096): 52.3e6,
-    ("mxfp4", 64, 57344, 8192): 256.1e6,
-    ("nvfp4", 8192, 3584, 8192): 95.5e6,
-    ("bf16", 1024, 1024, 1024): 4.2e6,
-    ("s8", 8192, 1024, 8192): 81.0e6,
+    ("nvfp4", 8192, 28672, 8192): 737e6,   # profiles/gemm_kernel_c4_nvfp4_8192x28672x8192.md
+    ("e4m3", 4096, 4096, 4096): 52.3e6,    # profiles/gemm_kernel_c2_e4m3_4096.md
+    ("mxfp4", 64, 57344, 8192): 252.0e6,   # profiles/gemm_kernel_c5_mxfp4_decode_64x57344x8192.md
 }
 
 Operands = namedtuple("Operands", "a b sfa sfb sfa_raw sfb_raw")
