@@ -107,7 +107,16 @@ OG_API int32_t og_smm_launch(const OgGemm* g, const void* a, const void* b, cons
  * reference's numbering (opengemm/src/mm/types.cuh:78-84): 0 bands `supergroup`
  * tiles wide along N; 1 the same, serpentine; 2 blocks inside a band; 3 a
  * generalised Hilbert curve; 4 bands along M.  Block-scaled formats, whose
- * reference struct carries no walk, use 0. */
+ * reference struct carries no walk, use 0.
+ *
+ * Cluster-K: OgGemm.cluster_k = 2, 4 or 8 with use_2cta = 0 makes that many CTAs of one
+ * thread-block cluster share every output tile, each taking a contiguous slice of K; the
+ * slices' accumulators meet in the shared memory of the cluster's first CTA (distributed
+ * shared memory, no trip through global memory), which stores the tile.  For shapes with
+ * fewer tiles than SMs (small M, decode).  The reference's cluster_k planes add into a
+ * zeroed C with atomics instead (opengemm/src/mm/kernel.cuh:29-36,86-96).  The request is
+ * lowered to what fits: no more ways than K blocks, and the landing zone of
+ * (cluster_k - 1) x tile width x 512 bytes must leave a three-stage ring. */
 
 /* The native tile plan of a bound GEMM, for tuners and reports. */
 typedef struct {
@@ -123,6 +132,7 @@ typedef struct {
   int32_t stream_k;  /* partial wave cut along K across clusters (split_k >= 2) */
   int32_t use_clc;   /* tiles handed out by cluster launch control; grid = one cluster per tile */
   int32_t fixed_shape; /* served by a kernel compiled for exactly this tile shape (og_b200_set_fixed_kernels) */
+  int32_t cluster_k; /* CTAs of a cluster sharing each tile along K (OgGemm.cluster_k with use_2cta = 0), else 1 */
 } OgPlan;
 
 /* Describe how `g` (already bound by og_mm_bind / og_smm_bind) would run on `device`

@@ -130,7 +130,7 @@ std::atomic<int> fixed_kernels_on{[] { const char* e = getenv("OPENGEMM_FIXED");
 int fixed_kernel_for(const Plan& p, const GemmParams& params) {
   if (!fixed_kernels_on.load(std::memory_order_relaxed)) return -1;
   if (params.transpose_out || !params.vec_ok || params.use_clc || params.stream_k || params.scale_out ||
-      params.bias || params.out_f16 || params.out_quant || params.walk)
+      params.bias || params.out_f16 || params.out_quant || params.walk || params.cluster_k > 1)
     return -1;
   const int epi = params.epi_tma ? 2 : params.epi_staged ? 1 : 0;
   for (int i = 0; i < FIXED_DENSE_COUNT + FIXED_SCALED_COUNT; ++i) {
@@ -232,14 +232,15 @@ void release_workspace(int device, int slot, cudaStream_t stream) {
 // tiles of the partial wave are then cut along K across all clusters.
 bool use_stream_k(const OgGemm& g, const Plan& p, int grid) {
   const int clusters = grid / p.cta_group;
-  return g.split_k >= 2 && p.num_tiles % clusters != 0 && p.k_blocks > 1;
+  return g.split_k >= 2 && p.cluster_k == 1 && p.num_tiles % clusters != 0 && p.k_blocks > 1;
 }
 
 int grid_for(const Plan& p, int sm_count, bool fill = false) {
   // `fill`: a stream-K launch occupies every SM even with fewer tiles than SMs.
-  const int all = std::max(1, sm_count / p.cta_group);
+  const int per_cluster = p.cta_group * p.cluster_k;
+  const int all = std::max(1, sm_count / per_cluster);
   const int clusters = fill ? std::min(all, std::max(1, p.num_tiles * p.k_blocks)) : std::max(1, std::min(p.num_tiles, all));
-  return clusters * p.cta_group;
+  return clusters * per_cluster;
 }
 
 int bind_impl(OgGemm* g, bool scaled) {
@@ -304,7 +305,7 @@ int launch_impl(const OgGemm* g, const LaunchPointers& io, int device, void* str
   const cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int sm_count = sm_count_of(device);
   int grid = grid_for(p, sm_count);
-  if (g->use_clc && g->split_k < 2) {
+  if (g->use_clc && g->split_k < 2 && p.cluster_k == 1) {
     // Cluster launch control: one cluster per tile; running clusters take over
     // the tiles of those that have not started.
     params.use_clc = 1;
@@ -323,7 +324,6 @@ int launch_impl(const OgGemm* g, const LaunchPointers& io, int device, void* str
       const int leftover = p.num_tiles % clusters;
       params.sk_clusters = std::min<long long>(clusters, (long long)leftover * std::min<int>(g->split_k, p.k_blocks));
     }
-    params.acc_int = p.format->out == OUT_S32;
   }
   const int fixed = fixed_kernel_for(p, params);
   if (fixed >= 0) {
@@ -419,7 +419,7 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
   out->grid = grid_for(p, sm_count_of(device));
   out->group = p.group;
   out->use_clc = 0;
-  if (g->use_clc && g->split_k < 2) {
+  if (g->use_clc && g->split_k < 2 && p.cluster_k == 1) {
     out->use_clc = 1;
     out->grid = p.num_tiles * p.cta_group;
   }
@@ -435,6 +435,8 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
     probe.tile_n = p.tile_n, probe.stages = p.stages, probe.epi_staged = p.epi_staged, probe.epi_tma = p.epi_tma;
     probe.transpose_out = p.swap, probe.walk = p.walk, probe.use_clc = out->use_clc, probe.stream_k = out->stream_k;
     probe.vec_ok = (int64_t(g->n) * p.out_bytes) % 16 == 0;
+    probe.cluster_k = p.cluster_k;
+    out->cluster_k = p.cluster_k;
     probe.out_f16 = p.format->out == OUT_F16;
     out->fixed_shape = fixed_kernel_for(p, probe) >= 0 ? 1 : 0;
   }
@@ -532,12 +534,12 @@ OG_API int32_t og_b200_describe(const OgGemm* g, int32_t sm_count, char* out, in
       "\"num_tiles\":%d,\"group\":%d,\"idesc\":%u,\"acc_slots\":%d,\"acc_stride\":%d,\"sf_col\":%d,\"sf_slots\":%d,"
       "\"sf_cols\":%d,\"tmem_cols\":%d,\"epi_staged\":%d,\"epi_tma\":%d,\"out_bytes\":%d,\"out\":%d,\"sf_atoms\":%d,\"sf_yblocks\":%d,"
       "\"k_groups\":%d,\"smem_bytes\":%d,\"x_bits\":%d,\"y_bits\":%d,\"x_map\":%d,\"y_map\":%d,\"l2_promo\":%d,"
-      "\"grid\":%d,\"m\":%d,\"n\":%d,\"walk\":%d}",
+      "\"grid\":%d,\"m\":%d,\"n\":%d,\"walk\":%d,\"cluster_k\":%d}",
       int(p.format->scaled), p.variant, p.format->kind, p.cta_group, p.swap, p.rows_m, p.rows_n, p.k, p.tile_m,
       p.tile_n, p.block_k, p.mma_k, p.k_blocks, p.stages, p.x_bytes, p.y_bytes, p.sf_bytes, p.stage_bytes,
       p.tx_bytes, p.tiles_m, p.tiles_n, p.num_tiles, p.group, p.idesc, p.acc_slots, p.acc_stride, p.sf_col,
       p.sf_slots, p.sf_cols, p.tmem_cols, p.epi_staged, p.epi_tma, p.out_bytes, p.format->out, p.sf_atoms, p.sf_yblocks,
-      p.k_groups, p.smem_bytes, p.x_bits, p.y_bits, p.x_map, p.y_map, p.l2_promo, grid, g->m, g->n, p.walk);
+      p.k_groups, p.smem_bytes, p.x_bits, p.y_bits, p.x_map, p.y_map, p.l2_promo, grid, g->m, g->n, p.walk, p.cluster_k);
   if (wrote < 0 || wrote >= cap) return fail(OG_ERR_BIND, "the buffer of %d bytes is too small for the description", cap);
   return OG_OK;
 }

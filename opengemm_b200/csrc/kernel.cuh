@@ -88,6 +88,10 @@ struct alignas(64) GemmParams {
   // Block-scaled output (2-byte-output kernels only): C leaves quantised along
   // N, ready to be the A operand of the next block-scaled GEMM.  `d` then
   // receives the packed values and `out_scales` the 128x4 blocked scales.
+  // Cluster-K (one-CTA MMAs only): `cluster_k` CTAs of a cluster share every
+  // tile, each taking a contiguous slice of its K blocks; ranks above 0 send
+  // their accumulators to rank 0's shared memory, which adds them and stores.
+  int cluster_k;          // 1 off, else 2, 4 or 8
   int out_quant;          // 0 off, else 1 + QFormat: 1 nvfp4, 2 mxfp8, 3 mxfp4
   int out_k_groups;       // 512-byte scale atoms along N of `out_scales`
   uint8_t* out_scales;
@@ -136,6 +140,7 @@ struct ClcState {
 };
 
 struct WorkIter {
+  int slice_kb0, slice_kb1;  // this CTA's K blocks of every tile (all of them unless cluster-K splits K)
   int stream_k, k_blocks, clusters, cluster, step;
   int tile, static_tiles;
   long long total, u, u_end;
@@ -143,9 +148,11 @@ struct WorkIter {
   ClcState clc;
   // `clusters` below is the number of clusters that share the partial wave
   // (p.sk_clusters, at most the grid's); `step` is the grid's cluster count.
-  __device__ __forceinline__ WorkIter(const GemmParams& p, int cluster_, int grid_clusters) {
+  __device__ __forceinline__ WorkIter(const GemmParams& p, int cluster_, int grid_clusters, int k_rank = 0) {
     stream_k = p.stream_k;
     k_blocks = p.k_blocks;
+    slice_kb0 = p.cluster_k > 1 ? p.k_blocks * k_rank / p.cluster_k : 0;
+    slice_kb1 = p.cluster_k > 1 ? p.k_blocks * (k_rank + 1) / p.cluster_k : p.k_blocks;
     step = grid_clusters;
     clusters = stream_k ? p.sk_clusters : grid_clusters;
     cluster = cluster_;
@@ -204,7 +211,7 @@ struct WorkIter {
   __device__ __forceinline__ bool next(Work& w) {
     if (use_clc) return next_clc(w);
     if (tile < static_tiles) {
-      w = {tile, 0, k_blocks};
+      w = {tile, slice_kb0, slice_kb1};
       tile += step;
       return true;
     }
@@ -262,7 +269,7 @@ __device__ __forceinline__ void fold_tile_shape(GemmParams& p) {
   p.sf_atoms = T::sf_atoms, p.sf_yblocks = T::sf_yblocks;
   p.epi_staged = T::epi_staged, p.epi_tma = T::epi_tma;
   p.transpose_out = 0, p.vec_ok = 1, p.walk = 0;
-  p.use_clc = 0, p.stream_k = 0, p.scale_out = 0, p.out_f16 = 0, p.out_quant = 0;
+  p.use_clc = 0, p.stream_k = 0, p.scale_out = 0, p.out_f16 = 0, p.out_quant = 0, p.cluster_k = 1;
   p.bias = nullptr;
 }
 #endif
@@ -293,7 +300,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   constexpr int TILE_M = 128 * CTA_GROUP;
 
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4 + 2 * CLC_SLOTS + 1];
+  __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4 + 2 * CLC_SLOTS + 1 + 8];
   __shared__ __align__(16) uint4 clc_answers[CLC_SLOTS];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -301,8 +308,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = (CTA_GROUP == 2) ? cluster_cta_rank() : 0u;
-  const int cluster_id = blockIdx.x / CTA_GROUP;
-  const int num_clusters = gridDim.x / CTA_GROUP;
+  // Cluster-K: `cluster_k` one-CTA MMAs form a cluster that shares each tile along K.
+  const int cluster_k = (CTA_GROUP == 1 && p.cluster_k > 1) ? p.cluster_k : 1;
+  const int k_rank = cluster_k > 1 ? int(cluster_cta_rank()) : 0;
+  const int cluster_id = blockIdx.x / (CTA_GROUP * cluster_k);
+  const int num_clusters = gridDim.x / (CTA_GROUP * cluster_k);
 
   const uint32_t ring = (smem_u32(dyn_smem) + SWIZZLE_ALIGN - 1) & ~uint32_t(SWIZZLE_ALIGN - 1);
   const uint32_t epi_base = ring + p.stages * p.stage_bytes;
@@ -313,6 +323,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   const uint32_t bar_clc_full = bar_acc_empty + 16;
   const uint32_t bar_clc_empty = bar_clc_full + 8 * CLC_SLOTS;
   const uint32_t bar_tmem = bar_clc_empty + 8 * CLC_SLOTS;  // tensor memory of every CTA of the pair is allocated
+  const uint32_t bar_ck_partial = bar_tmem + 8;    // rank 0, per epilogue warp: the other ranks' partial sums have arrived
+  const uint32_t bar_ck_free = bar_ck_partial + 32;  // ranks above 0, per epilogue warp: rank 0 has consumed them
+  // Rank 0's landing zone for the other ranks' accumulators, behind the epilogue's staging buffers.
+  const uint32_t ck_buffer = epi_base + (p.epi_staged ? 4 * (p.epi_tma ? 2 : 1) * EPI_BUF_BYTES : 0);
 
   const WaitCtx ctx{&abort_flag, p.status, p.wait_limit_ns};
 
@@ -343,11 +357,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       }
     }
     mbar_init(bar_tmem, CTA_GROUP);
+    if (cluster_k > 1) {
+      for (int q = 0; q < 4; ++q) {
+        mbar_init(bar_ck_partial + 8 * q, cluster_k - 1);
+        mbar_init(bar_ck_free + 8 * q, 1);
+      }
+    }
     abort_flag = 0;
     mbar_init_fence();
   }
   __syncthreads();
-  if constexpr (CTA_GROUP == 2) cluster_sync_all();
+  if (CTA_GROUP == 2 || cluster_k > 1) cluster_sync_all();
   if (warp == 1) {
     tmem_alloc<CTA_GROUP>(smem_u32(&tmem_slot), p.tmem_cols);
     tmem_relinquish<CTA_GROUP>();
@@ -388,7 +408,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       uint32_t phase = 0;
       uint32_t issued = 0;
       bool ok = true;
-      WorkIter work(p, cluster_id, num_clusters);
+      WorkIter work(p, cluster_id, num_clusters, k_rank);
       if (p.use_clc) work.enable_clc(clc_state(rank == 0, true), CTA_GROUP);
       Work w;
       while (ok && work.next(w)) {
@@ -445,7 +465,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     // scale copies and the four MMAs of a stage are fully unrolled.
     if (rank != 0) {
       if (p.use_clc && elect_one()) {  // the peer's idle warp still reads every answer
-        WorkIter work(p, cluster_id, num_clusters);
+        WorkIter work(p, cluster_id, num_clusters, k_rank);
         work.enable_clc(clc_state(false, true), CTA_GROUP);
         Work w;
         while (work.next(w)) {
@@ -471,7 +491,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       tc_fence_after_sync();
       const uint32_t tmem_base = tmem_slot;
       const uint32_t sf_base = tmem_base + p.sf_col;
-      WorkIter work(p, cluster_id, num_clusters);
+      WorkIter work(p, cluster_id, num_clusters, k_rank);
       if (p.use_clc) work.enable_clc(clc_state(false, true), CTA_GROUP);
       Work w;
       for (; ok && work.next(w); ++tile_idx) {
@@ -574,13 +594,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     // and its neighbour's (the same warp of the next cluster).
     const int my_region = (cluster_id * CTA_GROUP + int(rank)) * 4 + quarter;
     int last_sharer = 0;  // last cluster after this one that shares the tile being finished
-    WorkIter work(p, cluster_id, num_clusters);
+    WorkIter work(p, cluster_id, num_clusters, k_rank);
     if (p.use_clc) work.enable_clc(clc_state(false, lane == 0), CTA_GROUP);
     Work w;
     for (; __all_sync(0xFFFFFFFFu, allocated) && work.next(w); ++tile_idx) {
       const TileCoord t = tile_coord(p, w.tile);
-      const bool contributes = w.kb0 > 0;          // publish partial sums instead of output
-      const bool finishes = !contributes && w.kb1 < p.k_blocks;  // add the sharers' partials before storing
+      // Stream-K roles (a cluster-K rank also holds a K slice, but exchanges it through shared memory below).
+      const bool contributes = p.stream_k && w.kb0 > 0;          // publish partial sums instead of output
+      const bool finishes = p.stream_k && w.kb0 == 0 && w.kb1 < p.k_blocks;  // add the sharers' partials before storing
       const int slot = (p.acc_slots == 2) ? (tile_idx & 1) : 0;
       const uint32_t use = (p.acc_slots == 2) ? (tile_idx >> 1) : tile_idx;
       const bool ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
@@ -630,7 +651,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       bool handed_back = false, handed_back_late = false;
       if constexpr (OUT_BYTES == 2) {
         if (p.acc_slots == 1 && staged && tile_n == 256 && !contributes && !finishes && !scale_out && !bias && !out_f16 &&
-            !p.out_quant && row0 < rows_m) {
+            !p.out_quant && cluster_k == 1 && row0 < rows_m) {
           auto pack64 = [](const uint32_t* f, uint32_t* w) {
 #pragma unroll
             for (int u = 0; u < 32; ++u)
@@ -682,6 +703,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
             sharers_ready = wait_flag(p.flags + my_region + (j - cluster_id) * CTA_GROUP * 4, p.epoch, ctx);
           }
       }
+      // Cluster-K hand-shake for this tile: a rank above 0 may overwrite its part
+      // of rank 0's landing zone once rank 0 has consumed the previous tile's;
+      // rank 0 may read once every other rank's partial sums have arrived.
+      const bool ck_contributes = k_rank > 0, ck_finishes = cluster_k > 1 && k_rank == 0;
+      const bool ck_live = row0 < rows_m;  // warps whose rows lie past the matrix exchange no data
+      bool ck_ready = true;
+      if (ck_contributes && tile_idx > 0)
+        ck_ready = mbar_wait(bar_ck_free + 8 * quarter, (tile_idx - 1) & 1, ctx, SITE_CLUSTER_K);
+      if (ck_finishes) ck_ready = mbar_wait(bar_ck_partial + 8 * quarter, tile_idx & 1, ctx, SITE_CLUSTER_K);
+      if (!__all_sync(0xFFFFFFFFu, ck_ready)) sharers_ready = false;
+      auto ck_slot = [&](int peer, int c) {  // 16-byte vector g of row `lane` sits at (g * 32 + lane)
+        return ck_buffer + uint32_t((((peer * 4 + quarter) * (tile_n >> 2) + (c >> 2)) * 32 + lane) * 16);
+      };
       auto partial_of = [&](int j, int c) {
         return reinterpret_cast<const uint4*>(p.partial) +
                (size_t(my_region + (j - cluster_id) * CTA_GROUP * 4) * 64 + (c >> 2)) * 32 + lane;
@@ -752,6 +786,33 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
               }
             }
           }
+        }
+        if (ck_finishes && ck_live) {
+          for (int peer = 0; peer < cluster_k - 1; ++peer) {
+            const uint32_t src = ck_slot(peer, c);
+#pragma unroll
+            for (int u = 0; u < CHUNK / 4; ++u) {
+              if (4 * u >= width) continue;
+              const uint4 q = ld_shared_v4(src + u * 512);
+              if (p.acc_int) {
+                v[4 * u] += q.x, v[4 * u + 1] += q.y, v[4 * u + 2] += q.z, v[4 * u + 3] += q.w;
+              } else {
+                v[4 * u] = __float_as_uint(__uint_as_float(v[4 * u]) + __uint_as_float(q.x));
+                v[4 * u + 1] = __float_as_uint(__uint_as_float(v[4 * u + 1]) + __uint_as_float(q.y));
+                v[4 * u + 2] = __float_as_uint(__uint_as_float(v[4 * u + 2]) + __uint_as_float(q.z));
+                v[4 * u + 3] = __float_as_uint(__uint_as_float(v[4 * u + 3]) + __uint_as_float(q.w));
+              }
+            }
+          }
+        }
+        if (ck_contributes) {
+          if (ck_live) {
+            const uint32_t dst = map_to_cta(ck_slot(k_rank - 1, c), 0);
+#pragma unroll
+            for (int u = 0; u < CHUNK / 4; ++u)
+              if (4 * u < width) st_cluster_v4(dst + u * 512, make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]));
+          }
+          continue;
         }
         if (scale_out && !contributes) {  // the finished sum, scaled once; partial sums travel unscaled
 #pragma unroll
@@ -927,6 +988,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         __syncwarp();
         if (lane == 0) flag_release(p.flags + my_region, p.epoch);
       }
+      if (cluster_k > 1 && sharers_ready) {
+        // The arrive carries release semantics at cluster scope and follows the
+        // warp's synchronisation, so the partial sums written above (or, on rank
+        // 0, its reads of the landing zone) are ordered before it.
+        __syncwarp();
+        if (lane == 0) {
+          if (ck_contributes) mbar_arrive_cluster(map_to_cta(bar_ck_partial + 8 * quarter, 0));
+          else
+            for (int peer = 1; peer < cluster_k; ++peer) mbar_arrive_cluster(map_to_cta(bar_ck_free + 8 * quarter, peer));
+        }
+      }
       // A tile that left its loop early (nothing to store, or a give-up) still
       // hands the accumulator back.
       if (!handed_back && !handed_back_late) {
@@ -945,7 +1017,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   // ---------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
-  if constexpr (CTA_GROUP == 2) cluster_sync_all();
+  if (CTA_GROUP == 2 || cluster_k > 1) cluster_sync_all();
   tc_fence_after_sync();
   if (warp == 1) {
     __syncwarp();

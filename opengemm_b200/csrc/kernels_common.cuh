@@ -17,9 +17,10 @@ cudaError_t launch_one(const GemmParams& params, int grid, int smem_bytes, cudaS
   config.stream = stream;
   cudaLaunchAttribute attrs[2];
   int count = 0;
-  if (CTA_GROUP > 1) {  // a single CTA needs no cluster launch
+  const int cluster = CTA_GROUP * (params.cluster_k > 1 ? params.cluster_k : 1);  // the pair, or the CTAs sharing K
+  if (cluster > 1) {  // a single CTA needs no cluster launch
     attrs[count].id = cudaLaunchAttributeClusterDimension;
-    attrs[count].val.clusterDim.x = CTA_GROUP;
+    attrs[count].val.clusterDim.x = cluster;
     attrs[count].val.clusterDim.y = 1;
     attrs[count].val.clusterDim.z = 1;
     ++count;

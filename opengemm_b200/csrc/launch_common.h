@@ -237,6 +237,8 @@ inline int fill_params(const Plan& p, const OgGemm& g, const LaunchPointers& io,
   params.num_tiles = p.num_tiles;
   params.group = p.group;
   params.walk = p.walk;
+  params.cluster_k = p.cluster_k;
+  params.acc_int = p.format->out == OUT_S32;
   params.idesc = p.idesc;
   params.acc_slots = p.acc_slots;
   params.acc_stride = p.acc_stride;

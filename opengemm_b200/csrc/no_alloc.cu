@@ -165,9 +165,10 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
   // otherwise the plain schedule, which touches no workspace at all (and is
   // therefore never refused for its size).
   const cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int clusters = std::max(1, std::min(p.num_tiles, dev->sm_count / p.cta_group));
-  const int grid = clusters * p.cta_group;
-  if (p.num_tiles > clusters && p.num_tiles % clusters != 0 && p.k_blocks > 1) {
+  const int per_cluster = p.cta_group * p.cluster_k;
+  const int clusters = std::max(1, std::min(p.num_tiles, dev->sm_count / per_cluster));
+  const int grid = clusters * per_cluster;
+  if (p.cluster_k == 1 && p.num_tiles > clusters && p.num_tiles % clusters != 0 && p.k_blocks > 1) {
     const int regions = grid * 4;
     if (regions > MAX_REGIONS)
       return refuse(OG_ERR_LAUNCH,
@@ -187,7 +188,6 @@ OG_API int32_t og_b200_launch_no_alloc(const OgGemm* g, const void* a, const voi
     params.stream_k = 1;
     params.sk_clusters = clusters;
     params.epoch = int(tag & 0x7FFFFFFFu);
-    params.acc_int = p.format->out == OUT_S32;
     params.partial = reinterpret_cast<float*>(dev->workspace);
     params.flags = reinterpret_cast<int*>(flags);
   }

@@ -125,6 +125,7 @@ struct Plan {
   int tile_m = 128, tile_n = 128, block_k = 64, mma_k = 16, k_blocks = 0, stages = 0;
   int x_bytes = 0, y_bytes = 0, sf_bytes = 0, stage_bytes = 0, tx_bytes = 0;
   int tiles_m = 0, tiles_n = 0, num_tiles = 0, group = 1;
+  int cluster_k = 1;  // one-CTA MMAs only: CTAs of a cluster that share each tile along K (1, 2, 4 or 8)
   int walk = 0;       // rasterisation order (raster.h)
   int x_rows = 128;   // rows of the M-side box one CTA loads per stage
   uint32_t idesc = 0;
@@ -169,8 +170,11 @@ struct TileShape {
 // `smem_bits`: bits per value in shared memory (16 f16/bf16, 32 tf32, 8 for
 // every 8-bit container, 4 for packed fp4); `sf_block`: values per scale, 0
 // for a dense kind; `epi`: 0 each thread stores its own row, 1 rows staged in
-// shared memory, 2 staged and stored by TMA.
-constexpr TileShape tile_shape(int smem_bits, int sf_block, int cta_group, int out_bytes, int tile_n, int epi) {
+// shared memory, 2 staged and stored by TMA; `cluster_k`: CTAs sharing a tile
+// along K, whose accumulators land in (cluster_k - 1) x tile_n x 512 bytes of
+// rank 0's shared memory.
+constexpr TileShape tile_shape(int smem_bits, int sf_block, int cta_group, int out_bytes, int tile_n, int epi,
+                               int cluster_k = 1) {
   TileShape t;
   t.tile_n = tile_n;
   t.block_k = 1024 / smem_bits;
@@ -186,7 +190,7 @@ constexpr TileShape tile_shape(int smem_bits, int sf_block, int cta_group, int o
   t.stage_bytes = (t.x_bytes + t.y_bytes + t.sf_bytes + 1023) / 1024 * 1024;
   t.epi_staged = epi >= 1 ? 1 : 0;
   t.epi_tma = (epi == 2 && out_bytes == 4) ? 1 : 0;
-  const int epi_bytes = t.epi_staged ? 4 * (t.epi_tma ? 2 : 1) * (32 * 128) : 0;
+  const int epi_bytes = (t.epi_staged ? 4 * (t.epi_tma ? 2 : 1) * (32 * 128) : 0) + (cluster_k - 1) * tile_n * 512;
   const int fit = (227 * 1024 - (1024 + 512) - epi_bytes) / t.stage_bytes;
   t.stages = fit < 16 ? fit : 16;
   t.smem_bytes = t.stages * t.stage_bytes + epi_bytes + 1024;
@@ -267,7 +271,18 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
   const bool staged = !g.epi_direct && !p.swap && (ldd * p.out_bytes) % 16 == 0;
   const bool by_tma = staged && p.out_bytes == 4 && p.k_blocks >= 8 && p.tile_n % 32 == 0;
   p.epi = by_tma ? 2 : staged ? 1 : 0;
-  const TileShape t = tile_shape(smem_bits, f->scaled ? f->sf_block : 0, p.cta_group, p.out_bytes, p.tile_n, p.epi);
+  // Cluster-K: the requested power of two, no more ways than there are K
+  // blocks, halved until the landing zone leaves room for a three-stage ring.
+  p.cluster_k = 1;
+  if (p.cta_group == 1 && g.cluster_k > 1 && !g.use_clc && g.split_k < 2) {
+    int ways = 1;
+    while (ways * 2 <= std::min<int>(g.cluster_k, 8) && ways * 2 <= p.k_blocks) ways *= 2;
+    while (ways > 1 && tile_shape(smem_bits, f->scaled ? f->sf_block : 0, 1, p.out_bytes, p.tile_n, p.epi, ways).stages < 3)
+      ways /= 2;
+    p.cluster_k = ways;
+  }
+  const TileShape t =
+      tile_shape(smem_bits, f->scaled ? f->sf_block : 0, p.cta_group, p.out_bytes, p.tile_n, p.epi, p.cluster_k);
   p.block_k = t.block_k;
   p.mma_k = t.mma_k;
   p.x_bits = ex->value_bits;

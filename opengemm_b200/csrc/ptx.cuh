@@ -38,6 +38,7 @@ enum WaitSite : int {
   SITE_PARTIAL_FLAG = 6,
   SITE_CLC = 7,
   SITE_TMEM_READY = 8,
+  SITE_CLUSTER_K = 9,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -80,6 +80,8 @@ def refinements(config, tiles_n, fit_stages=0):
                 out.append(dict(config, stages=depth))
     out.append(dict(config, use_clc=True))
     out.append(dict(config, split_k=2))
+    if not config["use_2cta"]:  # few tiles: let 2, 4 or 8 CTAs of a cluster share each tile along K
+        out += [dict(config, cluster_k=ways) for ways in (2, 4, 8)]
     if "walk" in config:
         out += [dict(config, walk=1), dict(config, walk=3)]
     if not config["swap_ab"]:
@@ -91,14 +93,14 @@ def refinements(config, tiles_n, fit_stages=0):
 
 def simplicity(config):
     """Sort key under which the plainer configuration wins a tie."""
-    return (config["swap_ab"], 0 if config.get("split_k", 1) <= 1 else 1, int(bool(config.get("use_clc"))),
+    return (config["swap_ab"], 0 if config.get("split_k", 1) <= 1 else 1, config.get("cluster_k", 1), int(bool(config.get("use_clc"))),
             config.get("walk", 0), 0 if not config.get("stages") else 1, config.get("epi_direct", 0),
             config.get("l2_promo", 0), int(config["use_2cta"]), config["output_n"], config["supergroup"])
 
 
 def label(config):
     text = f"v{2 if config['use_2cta'] else 1} n{config['output_n']:<3} sg{config['supergroup']:<2} swap{int(config['swap_ab'])}"
-    for key in ("split_k", "epi_direct", "l2_promo", "stages", "walk", "use_clc"):
+    for key in ("split_k", "cluster_k", "epi_direct", "l2_promo", "stages", "walk", "use_clc"):
         if config.get(key, 0) not in (0, 1, False) or (key in ("epi_direct", "use_clc", "walk") and config.get(key)):
             text += f" {key}{int(config[key])}"
     return text
