@@ -158,10 +158,13 @@ struct WorkIter {
     cluster = cluster_;
     tile = cluster_;
     static_tiles = stream_k ? (p.num_tiles / grid_clusters) * grid_clusters : p.num_tiles;
-    total = (long long)(p.num_tiles - static_tiles) * p.k_blocks;
-    const bool shares = cluster_ < clusters;
-    u = shares ? total * cluster_ / clusters : 0;
-    u_end = shares ? total * (cluster_ + 1) / clusters : 0;
+    total = 0, u = 0, u_end = 0;
+    if (stream_k) {  // 64-bit divisions: kept off the static schedule's start-up path
+      total = (long long)(p.num_tiles - static_tiles) * p.k_blocks;
+      const bool shares = cluster_ < clusters;
+      u = shares ? total * cluster_ / clusters : 0;
+      u_end = shares ? total * (cluster_ + 1) / clusters : 0;
+    }
     use_clc = 0;
     answered = -1;
   }
