@@ -107,6 +107,8 @@ TRAFFIC_ENERGY = 0.25   # energy of moving a clock's worth of operand bytes, in 
 BOOST_GHZ, CAPPED_GHZ = 1.9, 1.35
 HBM_BYTES_PER_US = 6.5e6
 HBM_SATURATING_CTAS = 128.0
+LAUNCH_FLOOR_US = 4.0   # back-to-back launches of one tile take about this long each
+CTA_US = 0.004          # what a CTA costs the launches around it (ties go to fewer, fatter CTAs)
 
 
 def _smem_bytes_per_value(name):
@@ -159,6 +161,11 @@ def heuristic_config(name, m, n, k):
     """
     d = DTYPES[name]
     scaled = d.impl == "smm"
+    if scaled and d.bits == 4 and m <= 64 and n >= 1024:
+        # Block-scaled fp4 decode (tuned on 1..64 x 7168..57344 x 8192): 128 x 256 tiles
+        # on single CTAs, M on the padded 128-row side (rows past M are TMA zero fill and
+        # cost no traffic).  Few fat CTAs let consecutive launches run side by side.
+        return _with_defaults({"use_2cta": False, "output_n": 256, "swap_ab": False, "supergroup": 1}, scaled)
     swap = m <= 64 and n >= 2 * m
     rows_m, rows_n = (n, m) if swap else (m, n)
     # Widths that fill whole 128-byte lines of the staged rows.
@@ -178,17 +185,32 @@ def heuristic_config(name, m, n, k):
             if two and width < 32:
                 continue
             cost = modelled_us(name, m, n, k, two, width, swap)
+            # Measured corrections to the model: a launch is never shorter than the
+            # launch floor, below which fewer CTAs win (consecutive launches then run
+            # side by side); a 256-wide block-scaled pair tile, which has tensor memory
+            # for one accumulator only, loses a little more than the model's drain term
+            # says (192 won 9 of 12 tuned large block-scaled shapes).
+            ctas = -(-rows_m // (256 if two else 128)) * -(-rows_n // width) * (2 if two else 1)
+            cost = max(cost, LAUNCH_FLOOR_US) + CTA_US * min(ctas, SM_COUNT)
+            if scaled and two and width == 256:
+                cost *= 1.08
             if best is None or cost < best[0] * 0.98:
                 best = (cost, two, width)
     _, use_2cta, output_n = best
+    return _with_defaults({"use_2cta": bool(use_2cta), "output_n": int(output_n), "swap_ab": bool(swap), "supergroup": 8},
+                          scaled)
+
+
+def _with_defaults(knobs, scaled):
+    """A complete configuration in the store's schema from the knobs the heuristic decides."""
     config = {
-        "use_2cta": bool(use_2cta),
-        "output_n": int(output_n),
+        "use_2cta": bool(knobs["use_2cta"]),
+        "output_n": int(knobs["output_n"]),
         "use_clc": False,
-        "supergroup": 8,
-        "swap_ab": bool(swap),
+        "supergroup": int(knobs["supergroup"]),
+        "swap_ab": bool(knobs["swap_ab"]),
         "epi_direct": 0,
-        "cluster_m": 2 if use_2cta else 1,
+        "cluster_m": 2 if knobs["use_2cta"] else 1,
         "cluster_n": 1,
         "cluster_k": 1,
     }

@@ -103,8 +103,10 @@ def test_plan_of_the_baseline_configurations():
         lib, g = capi.bind(name, m, n, k, heuristic_config(name, m, n, k))
         plan = lib.plan(g)
         assert plan["grid"] <= 148 and plan["tiles"] >= 1
-        if m <= 64:
-            assert plan["swap"] == 1  # small M rides the MMA's N side
+        if m <= 64:  # block-scaled fp4 decode: M on the padded 128-row side of fat single-CTA tiles
+            assert (plan["swap"], plan["cta_group"], plan["tile_n"]) == (0, 1, 256)
+    lib, g = capi.bind("e4m3", 16, 8192, 4096, heuristic_config("e4m3", 16, 8192, 4096))
+    assert lib.plan(g)["swap"] == 1  # other formats: small M rides the MMA's N side
 
 
 def test_plan_invariants_over_the_shape_suite():

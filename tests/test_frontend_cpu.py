@@ -138,15 +138,21 @@ def test_the_shape_suite_lists_the_headline_configurations():
 
 def test_heuristic_configurations_follow_the_tile_time_model():
     """Wide pair tiles for long-K compute-bound shapes, single CTAs once the
-    output stores dominate, operand swap for decode shapes; every choice binds."""
+    output stores dominate, operand swap for small M, the measured corrections
+    (fp4 decode, block-scaled tile width, launch-bound shapes); every choice binds."""
     from opengemm_b200 import capi
     from opengemm_b200.configs import heuristic_config, load_shapes, modelled_us
 
     big = heuristic_config("e4m3", 8192, 8192, 8192)
     assert big["use_2cta"] and big["output_n"] == 256 and not big["swap_ab"]
     assert not heuristic_config("bf16", 8192, 8192, 32)["use_2cta"]
-    decode = heuristic_config("mxfp4", 64, 57344, 8192)
-    assert decode["swap_ab"] and decode["output_n"] == 64
+    decode = heuristic_config("mxfp4", 64, 57344, 8192)   # fp4 decode: fat single-CTA tiles, no swap
+    assert not decode["swap_ab"] and not decode["use_2cta"] and decode["output_n"] == 256
+    assert heuristic_config("e4m3", 16, 8192, 4096)["swap_ab"]   # other small-M shapes ride the N side
+    scaled = heuristic_config("nvfp4", 8192, 14336, 8192)       # two accumulators beat one 256-wide tile
+    assert scaled["use_2cta"] and scaled["output_n"] == 192
+    tiny = heuristic_config("bf16", 128, 128, 128)               # launch-bound: one fat CTA, not four thin ones
+    assert not tiny["use_2cta"] and tiny["output_n"] == 128
     # a narrow tile never models faster than the full-width pair tile on a long-K square
     assert modelled_us("bf16", 8192, 8192, 8192, True, 64, False) > modelled_us("bf16", 8192, 8192, 8192, True, 256, False)
     for name in ("bf16", "s8", "e2m3", "nvfp4", "mxfp8", "mxfp4"):
