@@ -133,6 +133,7 @@ typedef struct {
   int32_t use_clc;   /* tiles handed out by cluster launch control; grid = one cluster per tile */
   int32_t fixed_shape; /* served by a kernel compiled for exactly this tile shape (og_b200_set_fixed_kernels) */
   int32_t cluster_k; /* CTAs of a cluster sharing each tile along K (OgGemm.cluster_k with use_2cta = 0), else 1 */
+  int32_t plain;     /* served by the build of the run-time-shaped kernel that has no optional feature compiled in */
 } OgPlan;
 
 /* Describe how `g` (already bound by og_mm_bind / og_smm_bind) would run on `device`
@@ -226,11 +227,16 @@ OG_API const char* og_b200_quantize_error(void);
  * (opengemm/src/mm/kernel.cuh:209,479-483).  Default 0. */
 OG_API void og_b200_set_independent_inputs(int32_t yes);
 
-/* The hot tile shapes (pairs of CTAs on 256-row tiles, the decode tile) also exist as
- * kernels compiled for that one shape, with the plan's constants folded in; a launch whose
- * plan equals one of them runs it, every other launch runs the run-time-planned kernel.
- * Both compute the same bits.  `yes` = 0 sends every launch to the run-time kernel
- * (default 1; the environment variable OPENGEMM_FIXED=0 sets the default to 0). */
+/* Specialised builds of the kernel.  The hot tile shapes (pairs of CTAs on 256-row tiles,
+ * the decode tile) also exist as kernels compiled for that one shape, with the plan's
+ * constants folded in; and every variant exists once more with a run-time tile shape but
+ * none of the optional features (stream-K, cluster launch control, cluster-K, bias, alpha,
+ * half or block-scaled output, the non-default tile walks) compiled in, which is what a
+ * launch that asks for none of them runs when no fixed-shape kernel matches its plan: a
+ * GEMM of a tile or two per CTA runs its code once, from a cold instruction cache, and is
+ * timed by the amount of code on its path.  All builds compute the same bits.  `yes` = 0
+ * sends every launch to the full run-time kernel (default 1; the environment variable
+ * OPENGEMM_FIXED=0 sets the default to 0). */
 OG_API void og_b200_set_fixed_kernels(int32_t yes);
 
 /* Limit of every device-side wait in milliseconds (default 2000).  Waits for a whole

@@ -31,7 +31,8 @@ ROOT = PACKAGE.parent
 CSRC = PACKAGE / "csrc"
 LIB_DIR = PACKAGE / "lib"
 LIB_NAME = "libopengemm_b200.so"
-UNITS = ("host", "kernels_dense", "kernels_scaled", "kernels_fixed_dense", "kernels_fixed_scaled", "no_alloc", "quantize")
+UNITS = ("host", "kernels_dense", "kernels_scaled", "kernels_fixed_dense", "kernels_fixed_scaled",
+         "kernels_plain_dense", "kernels_plain_scaled", "no_alloc", "quantize")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", *ARCH, "-Xcompiler", "-fPIC,-fvisibility=hidden"]

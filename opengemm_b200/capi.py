@@ -51,7 +51,7 @@ class OgPlan(ctypes.Structure):
         (f, c_int32)
         for f in (
             "cta_group", "tile_m", "tile_n", "block_k", "stages", "swap", "epi_staged", "epi_tma",
-            "acc_slots", "tmem_cols", "smem_bytes", "tiles", "grid", "group", "stream_k", "use_clc", "fixed_shape", "cluster_k",
+            "acc_slots", "tmem_cols", "smem_bytes", "tiles", "grid", "group", "stream_k", "use_clc", "fixed_shape", "cluster_k", "plain",
         )
     ]
 

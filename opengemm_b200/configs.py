@@ -86,6 +86,29 @@ def stored_entry(name, m, n, k):
     return None
 
 
+# Formats that run the same kernel instantiation on operands of the same width
+# in shared memory (csrc/plan.h FORMATS: MMA kind and container bits), so that a
+# configuration tuned for one is the right one for the others.
+KERNEL_FAMILIES = (
+    ("bf16", "f16"),
+    ("s8", "u8"),
+    ("e4m3", "e5m2", "e4m3xe5m2", "e3m2", "e2m3", "e2m1"),
+)
+
+
+def sibling_entry(name, m, n, k):
+    """The stored entry of a format of `name`'s kernel family for this shape
+    (the first member that has a usable one), or None."""
+    for family in KERNEL_FAMILIES:
+        if name in family:
+            for other in family:
+                if other != name:
+                    entry = stored_entry(other, m, n, k)
+                    if entry is not None and entry.get("config") is not None:
+                        return entry
+    return None
+
+
 def _round_up(x, to):
     return -(-x // to) * to
 
@@ -224,7 +247,8 @@ def _with_defaults(knobs, scaled):
 
 def resolve_config(name, m, n, k):
     """The configuration for a (dtype, shape): stored, else tuned now when
-    OPENGEMM_AUTOTUNE=1, else the heuristic.
+    OPENGEMM_AUTOTUNE=1, else what is stored for a format of the same kernel
+    family (`KERNEL_FAMILIES`), else the heuristic.
 
     Raises:
         ValueError: if the shape is recorded as unimplementable.
@@ -236,6 +260,9 @@ def resolve_config(name, m, n, k):
 
             log(f"no stored configuration for {name} {m}x{n}x{k}; tuning it now")
             return tune(name, m, n, k)
+        entry = sibling_entry(name, m, n, k)
+        if entry is not None:
+            return entry["config"]
         return heuristic_config(name, m, n, k)
     if entry.get("config") is None:
         why = entry.get("unimplementable", "recorded as unimplementable")

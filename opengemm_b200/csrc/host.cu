@@ -39,9 +39,21 @@ extern const FixedKernel FIXED_DENSE[];
 extern const int FIXED_DENSE_COUNT;
 extern const FixedKernel FIXED_SCALED[];
 extern const int FIXED_SCALED_COUNT;
+// Implemented in kernels_plain_dense.cu and kernels_plain_scaled.cu.
+extern const FixedKernel PLAIN_DENSE[];
+extern const int PLAIN_DENSE_COUNT;
+extern const FixedKernel PLAIN_SCALED[];
+extern const int PLAIN_SCALED_COUNT;
 
+// One index space over the specialised kernels: fixed-shape dense, fixed-shape
+// scaled, then the feature-free ones.
+inline int fixed_count() { return FIXED_DENSE_COUNT + FIXED_SCALED_COUNT; }
+inline int specialised_count() { return fixed_count() + PLAIN_DENSE_COUNT + PLAIN_SCALED_COUNT; }
 inline const FixedKernel& fixed_kernel(int index) {
-  return index < FIXED_DENSE_COUNT ? FIXED_DENSE[index] : FIXED_SCALED[index - FIXED_DENSE_COUNT];
+  if (index < FIXED_DENSE_COUNT) return FIXED_DENSE[index];
+  if (index < fixed_count()) return FIXED_SCALED[index - FIXED_DENSE_COUNT];
+  index -= fixed_count();
+  return index < PLAIN_DENSE_COUNT ? PLAIN_DENSE[index] : PLAIN_SCALED[index - PLAIN_DENSE_COUNT];
 }
 
 inline cudaError_t configure_variant(int variant, int smem_bytes) {
@@ -122,24 +134,29 @@ int sm_count_of(int device) {
   return info.sm_count;
 }
 
-// The kernel compiled for exactly this launch's tile shape, if there is one:
-// its index, else -1.  Every value such a kernel has folded in must equal the
-// launch's, and every option it was compiled without must be off.
+// The most specialised kernel that serves this launch: the one compiled for
+// exactly its tile shape if there is one, else - when it asks for no optional
+// feature - the feature-free build of its variant; its index, else -1.  Every
+// value such a kernel has folded in must equal the launch's, and every option
+// it was compiled without must be off.
 std::atomic<int> fixed_kernels_on{[] { const char* e = getenv("OPENGEMM_FIXED"); return (e && e[0] == '0') ? 0 : 1; }()};
 
 int fixed_kernel_for(const Plan& p, const GemmParams& params) {
   if (!fixed_kernels_on.load(std::memory_order_relaxed)) return -1;
-  if (params.transpose_out || !params.vec_ok || params.use_clc || params.stream_k || params.scale_out ||
-      params.bias || params.out_f16 || params.out_quant || params.walk || params.cluster_k > 1)
+  if (params.use_clc || params.stream_k || params.scale_out || params.bias || params.out_f16 || params.out_quant ||
+      params.walk || params.cluster_k > 1)
     return -1;
   const int epi = params.epi_tma ? 2 : params.epi_staged ? 1 : 0;
-  for (int i = 0; i < FIXED_DENSE_COUNT + FIXED_SCALED_COUNT; ++i) {
+  for (int i = 0; i < fixed_count() && !params.transpose_out && params.vec_ok; ++i) {
     const FixedKernel& k = fixed_kernel(i);
     if (k.variant != p.variant || k.tile_n != params.tile_n || k.epi != epi) continue;
     const TileShape t = tile_shape(p.smem_bits, p.format->scaled ? p.format->sf_block : 0, p.cta_group,
                                    p.out_bytes, k.tile_n, k.epi);
-    return t.stages == params.stages ? i : -1;
+    if (t.stages == params.stages) return i;
+    break;
   }
+  for (int i = fixed_count(); i < specialised_count(); ++i)
+    if (fixed_kernel(i).variant == p.variant) return i;
   return -1;
 }
 
@@ -438,7 +455,9 @@ OG_API int32_t og_b200_plan(const OgGemm* g, int32_t device, OgPlan* out) {
     probe.cluster_k = p.cluster_k;
     out->cluster_k = p.cluster_k;
     probe.out_f16 = p.format->out == OUT_F16;
-    out->fixed_shape = fixed_kernel_for(p, probe) >= 0 ? 1 : 0;
+    const int special = fixed_kernel_for(p, probe);
+    out->fixed_shape = (special >= 0 && special < fixed_count()) ? 1 : 0;
+    out->plain = special >= fixed_count() ? 1 : 0;
   }
   return OG_OK;
 }
@@ -493,7 +512,7 @@ OG_API int32_t og_b200_prepare_device(int32_t device) {
     const int configured = ensure_configured(device, variant, 0);
     if (configured != OG_OK) return configured;
   }
-  for (int index = 0; index < FIXED_DENSE_COUNT + FIXED_SCALED_COUNT; ++index) {
+  for (int index = 0; index < specialised_count(); ++index) {
     const int configured = ensure_fixed_configured(device, index);
     if (configured != OG_OK) return configured;
   }

@@ -97,6 +97,18 @@ struct alignas(64) GemmParams {
   uint8_t* out_scales;
 };
 
+// Second, unused kernel argument.  On B200 with driver 580 the host cost of
+// cudaLaunchKernelEx depends on the size of the parameter block modulo 64: an
+// empty kernel launches in 1.7 us per call with 416, 480, 544, ... 928 or 992
+// bytes of parameters and in 2.0-2.2 us with any multiple of 64 from 448 to
+// 1024 (measured back to back on three machines).  GemmParams is a multiple of
+// 64 because tensor maps are 64-byte aligned; these 32 bytes move the block to
+// the cheap residue, which is the difference a launch-bound GEMM sees.
+struct LaunchPad {
+  unsigned long long words[4];
+};
+static_assert((sizeof(GemmParams) + sizeof(LaunchPad)) % 64 == 32, "parameter block should be an odd multiple of 32 bytes");
+
 // Tiles are visited in the order `walk` names (raster.h); the default is bands
 // `group` tiles wide along N, N fastest inside a band, so concurrently running
 // clusters share X rows and Y rows in L2.
@@ -275,13 +287,28 @@ __device__ __forceinline__ void fold_tile_shape(GemmParams& p) {
   p.use_clc = 0, p.stream_k = 0, p.scale_out = 0, p.out_f16 = 0, p.out_quant = 0, p.cluster_k = 1;
   p.bias = nullptr;
 }
+
+// What a launch without any optional feature leaves unused: folding these to
+// constants removes the stream-K, cluster launch control, cluster-K, bias,
+// scaling, half and block-scaled output code and all tile walks but the
+// default from the kernel.  The tile shape stays a run-time value.
+__device__ __forceinline__ void fold_features_off(GemmParams& p) {
+  p.walk = 0, p.use_clc = 0, p.stream_k = 0, p.scale_out = 0, p.out_f16 = 0, p.out_quant = 0, p.cluster_k = 1;
+  p.bias = nullptr;
+}
 #endif
 
 // FIXED_N == 0: every tile-plan value is read from `params` at run time.
 // FIXED_N != 0: the kernel is compiled for tiles FIXED_N wide with epilogue
 // path FIXED_EPI (0 each thread its own row, 1 staged rows, 2 TMA stores).
-template <int KIND, int CTA_GROUP, int OUT_BYTES, int FIXED_N = 0, int FIXED_EPI = 0>
-__global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams params) {
+// PLAIN: compiled without the optional features (fold_features_off).  A GEMM
+// of one or two tiles per CTA executes most of its instructions once, straight
+// from a cold instruction cache, so its time follows the amount of code on
+// the path it takes: bf16 128^3 spends 2.2 us between the previous grid's
+// completion and its own in the full kernel, 1.5 us in the plain one and
+// 1.0 us in one compiled for its tile shape.
+template <int KIND, int CTA_GROUP, int OUT_BYTES, int FIXED_N = 0, int FIXED_EPI = 0, bool PLAIN = false>
+__global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant__ GemmParams params, const LaunchPad) {
   // `p` is the scalar view of the launch parameters.  A standalone kernel
   // emitted for one shape defines OG_FIXED_PLAN to overwrite the plan fields
   // of a local copy with literals, which lets the compiler fold them; tensor
@@ -295,6 +322,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
   if constexpr (FIXED_N != 0) {
     folded = params;
     fold_tile_shape<KIND, CTA_GROUP, OUT_BYTES, FIXED_N, FIXED_EPI>(folded);
+    view = &folded;
+  } else if constexpr (PLAIN) {
+    folded = params;
+    fold_features_off(folded);
     view = &folded;
   }
   const GemmParams& p = *view;
@@ -610,8 +641,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       const bool ready = mbar_wait(bar_acc_full + 8 * slot, use & 1, ctx, SITE_EPI_ACC_FULL);
       if (!__all_sync(0xFFFFFFFFu, ready)) break;
       tc_fence_after_sync();
-      if (p.pdl && !touched_memory) pdl_wait_prior_grids();
-      touched_memory = true;
+      // The previous grid is waited for as late as possible: by whichever path
+      // below first touches global memory, with its accumulators already in
+      // registers where it can.
+      auto before_global_memory = [&] {
+        if (p.pdl && !touched_memory) pdl_wait_prior_grids();
+        touched_memory = true;
+      };
 
       const int row0 = t.mi * TILE_M + int(rank) * 128 + quarter * 32;  // first row of this warp
       const int row = row0 + lane;
@@ -666,6 +702,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           tmem_ld_settle_32(va), tmem_ld_settle_32(va + 32);
           tmem_ld_32(acc_tmem + 64, vb), tmem_ld_32(acc_tmem + 96, vb + 32);
           pack64(va, held);
+          before_global_memory();
           store_staged(held, 0, 64);
           tmem_ld_wait();
           tmem_ld_settle_32(vb), tmem_ld_settle_32(vb + 32);
@@ -699,6 +736,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
       int first_sharer = 0;
       bool sharers_ready = true;
       if (finishes) {
+        before_global_memory();
         last_sharer = work.last_sharer(w);
         for (int j = cluster_id + 1; j <= last_sharer && sharers_ready; ++j)
           if (work.has_work(j)) {
@@ -730,9 +768,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         for (int u = 0; u < CHUNK / 4; ++u) ahead[AHEAD ? u : 0] = (4 * u < tile_n) ? __ldcg(src + u * 32) : make_uint4(0u, 0u, 0u, 0u);
       }
 
-      for (int c = 0; !handed_back && sharers_ready && c < tile_n && col0 + c < rows_n; c += CHUNK) {
+      // 32-bit output: the loads of the next chunk are in flight while this
+      // one is converted and stored (one chunk of registers ahead), so a tile's
+      // drain costs the stores rather than stores plus tensor-memory latency -
+      // which is what a launch-bound GEMM's tail, and every last tile, is made of.
+      constexpr bool PIPELINED = OUT_BYTES == 4;
+      auto chunk_live = [&](int c) { return c < tile_n && col0 + c < rows_n; };
+      auto issue_loads = [&](int c, uint32_t* v) {
         const int width = min(CHUNK, tile_n - c);
-        uint32_t v[CHUNK];
         if (width >= 32) tmem_ld_32(acc_tmem + c, v);
         else tmem_ld_16(acc_tmem + c, v);
         if constexpr (CHUNK == 64) {
@@ -741,8 +784,29 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
             else tmem_ld_16(acc_tmem + c + 32, v + 32);
           }
         }
-        tmem_ld_wait();
-        if (c + CHUNK >= tile_n || col0 + c + CHUNK >= rows_n) {
+      };
+      const bool drains = !handed_back && sharers_ready;
+      uint32_t coming[PIPELINED ? CHUNK : 1];
+      if constexpr (PIPELINED) {
+#pragma unroll
+        for (int j = 0; j < CHUNK; ++j) coming[j] = 0u;
+        if (drains && chunk_live(0)) issue_loads(0, coming);
+      }
+      for (int c = 0; drains && chunk_live(c); c += CHUNK) {
+        const int width = min(CHUNK, tile_n - c);
+        const bool last_chunk = !chunk_live(c + CHUNK);
+        uint32_t v[CHUNK];
+        if constexpr (PIPELINED) {
+          tmem_ld_wait();
+          tmem_ld_settle_32(coming);
+#pragma unroll
+          for (int j = 0; j < CHUNK; ++j) v[j] = coming[PIPELINED ? j : 0];
+          if (!last_chunk) issue_loads(c + CHUNK, coming);
+        } else {
+          issue_loads(c, v);
+          tmem_ld_wait();
+        }
+        if (last_chunk) {
           // The last columns are in registers: the accumulator goes back to
           // the MMA warp before they are converted and stored.
           tc_fence_before_sync();
@@ -753,6 +817,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           }
           handed_back_late = true;
         }
+        before_global_memory();
 
         if (finishes) {
           // Partial sums of every cluster that shares this tile.
@@ -1015,6 +1080,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
     }
     // Shared memory may be released once the last TMA stores have read it.
     if (tma_out && lane == 0) tma_store_wait_read<0>();
+    // Every grid waits for its predecessor before it ends, so that completion
+    // stays transitive along the stream even for a warp that stored nothing.
+    if (p.pdl && !touched_memory) pdl_wait_prior_grids();
   }
 
   // ---------------------------------------------------------------- teardown

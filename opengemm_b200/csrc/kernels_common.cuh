@@ -7,7 +7,7 @@
 
 namespace og {
 
-template <int KIND, int CTA_GROUP, int OUT_BYTES, int FIXED_N = 0, int FIXED_EPI = 0>
+template <int KIND, int CTA_GROUP, int OUT_BYTES, int FIXED_N = 0, int FIXED_EPI = 0, bool PLAIN = false>
 cudaError_t launch_one(const GemmParams& params, int grid, int smem_bytes, cudaStream_t stream,
                        bool pdl) {
   cudaLaunchConfig_t config = {};
@@ -32,12 +32,13 @@ cudaError_t launch_one(const GemmParams& params, int grid, int smem_bytes, cudaS
   }
   config.attrs = attrs;
   config.numAttrs = count;
-  return cudaLaunchKernelEx(&config, gemm_kernel<KIND, CTA_GROUP, OUT_BYTES, FIXED_N, FIXED_EPI>, params);
+  return cudaLaunchKernelEx(&config, gemm_kernel<KIND, CTA_GROUP, OUT_BYTES, FIXED_N, FIXED_EPI, PLAIN>, params,
+                            LaunchPad{});
 }
 
-template <int KIND, int CTA_GROUP, int OUT_BYTES, int FIXED_N = 0, int FIXED_EPI = 0>
+template <int KIND, int CTA_GROUP, int OUT_BYTES, int FIXED_N = 0, int FIXED_EPI = 0, bool PLAIN = false>
 cudaError_t configure_one(int smem_bytes) {
-  return cudaFuncSetAttribute(gemm_kernel<KIND, CTA_GROUP, OUT_BYTES, FIXED_N, FIXED_EPI>,
+  return cudaFuncSetAttribute(gemm_kernel<KIND, CTA_GROUP, OUT_BYTES, FIXED_N, FIXED_EPI, PLAIN>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
 }
 

@@ -22,4 +22,10 @@ struct FixedKernel {
 #define OG_FIXED_KERNEL(VARIANT, KIND, GROUP, OUT, N, EPI) \
   FixedKernel { VARIANT, N, EPI, configure_one<KIND, GROUP, OUT, N, EPI>, launch_one<KIND, GROUP, OUT, N, EPI> }
 
+// The run-time-shaped kernel of a variant compiled without the optional
+// features (tile_n and epi are unused in these rows): what every launch that
+// asks for none of them runs, unless a fixed-shape kernel serves its plan.
+#define OG_PLAIN_KERNEL(VARIANT, KIND, GROUP, OUT) \
+  FixedKernel { VARIANT, 0, 0, configure_one<KIND, GROUP, OUT, 0, 0, true>, launch_one<KIND, GROUP, OUT, 0, 0, true> }
+
 }  // namespace og

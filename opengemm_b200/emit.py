@@ -160,7 +160,7 @@ void launch(const void* a, const void* b, const void* sfa, const void* sfb, void
   attrs[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attrs;
   config.numAttrs = 2;
-  cudaLaunchKernelEx(&config, og::gemm_kernel<og::{kind}, {cta_group}, {out_bytes}>, cache.params);
+  cudaLaunchKernelEx(&config, og::gemm_kernel<og::{kind}, {cta_group}, {out_bytes}>, cache.params, og::LaunchPad{{}});
 }}
 
 }}  // namespace

@@ -92,6 +92,19 @@ def test_config_store_round_trip(tmp_path, monkeypatch):
     assert not list(tmp_path.glob("*.tmp"))
 
 
+def test_a_format_without_an_entry_takes_its_kernel_familys(tmp_path, monkeypatch):
+    monkeypatch.setenv("OPENGEMM_CONFIGS", str(tmp_path))
+    shape = (96, 200, 160)
+    odd = dict(configs.heuristic_config("e4m3", *shape), output_n=80, supergroup=3)
+    configs.write_entry("mm", {"dtype": "e4m3", "m": shape[0], "n": shape[1], "k": shape[2], "config": odd})
+    for name in ("e5m2", "e2m1", "e4m3xe5m2"):
+        assert configs.resolve_config(name, *shape) == odd
+    assert configs.resolve_config("bf16", *shape) == configs.heuristic_config("bf16", *shape)  # another kernel
+    own = dict(odd, output_n=96)
+    configs.write_entry("mm", {"dtype": "e5m2", "m": shape[0], "n": shape[1], "k": shape[2], "config": own})
+    assert configs.resolve_config("e5m2", *shape) == own  # its own entry wins
+
+
 def test_config_store_reads_a_file_in_the_references_schema(tmp_path, monkeypatch, golden_dir):
     sets = json.loads((golden_dir / "reference_config_knobs.json").read_text())
     ref_entry = dict(sets["mm"][0])
