@@ -216,6 +216,25 @@ class Library:
         if status != OG_OK:
             raise RuntimeError(self.error())
 
+    def launcher(self, g, a, b, sfa, sfb, out):
+        """A zero-argument callable that enqueues this launch on the current
+        stream of the operands' device each time it is called.  The bound GEMM
+        and the tensors' addresses are captured once (and the tensors kept
+        alive), which leaves about a third of `launch`'s interpreter time per
+        call: for loops that run the same buffers again and again, where a
+        small GEMM is otherwise timed by the wrapper around it."""
+        device = a.get_device()
+        args = (byref(g), a.data_ptr(), b.data_ptr(), 0 if sfa is None else sfa.data_ptr(),
+                0 if sfb is None else sfb.data_ptr(), out.data_ptr(), device)
+        launch = self._launch
+
+        def call():
+            if launch(*args, raw_stream(device)) != OG_OK:
+                raise RuntimeError(self.error())
+
+        call.keeps = (g, a, b, sfa, sfb, out)  # the addresses above stay valid as long as the callable lives
+        return call
+
     def launch_checked(self, g, a, b, sfa, sfb, out, status_word):
         """Like `launch`, with a zeroed int32 device tensor that receives a code
         if any device-side wait gives up."""

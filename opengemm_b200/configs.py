@@ -132,6 +132,8 @@ HBM_BYTES_PER_US = 6.5e6
 HBM_SATURATING_CTAS = 128.0
 LAUNCH_FLOOR_US = 4.0   # back-to-back launches of one tile take about this long each
 CTA_US = 0.004          # what a CTA costs the launches around it (ties go to fewer, fatter CTAs)
+PAIR_FROM_US = 9.0      # below this a pair's set-up (cluster synchronisation, both CTAs' tensor memory) shows ...
+PAIR_SETUP_US = 1.0     # ... as about this much
 
 
 def _smem_bytes_per_value(name):
@@ -217,6 +219,8 @@ def heuristic_config(name, m, n, k):
             cost = max(cost, LAUNCH_FLOOR_US) + CTA_US * min(ctas, SM_COUNT)
             if scaled and two and width == 256:
                 cost *= 1.08
+            if two and cost < PAIR_FROM_US:
+                cost += PAIR_SETUP_US  # single CTAs won 90 % of the tuned shapes that run under 9 us
             if best is None or cost < best[0] * 0.98:
                 best = (cost, two, width)
     _, use_2cta, output_n = best

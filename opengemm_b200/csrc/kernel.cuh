@@ -600,7 +600,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         (CTA_GROUP == 2) ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
     // One staging buffer per warp; two when they drain by TMA store, which
     // reads a buffer asynchronously while the next one is filled.
-    const bool tma_out = OUT_BYTES == 4 && p.epi_tma != 0;
+    const bool tma_out = p.epi_tma != 0;
     const uint32_t my_buf = epi_base + (warp - 2) * (tma_out ? 2 : 1) * EPI_BUF_BYTES;
     int buf_use = 0;
     constexpr int CHUNK = (OUT_BYTES == 2) ? 64 : 32;  // columns per 128-byte staging row
@@ -681,6 +681,38 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
         __syncwarp();
       };
 
+      // The same staged block handed to a TMA store, which clips it at the edges
+      // of D: the fewest instructions, the least power on a capped part, and
+      // more bytes in flight per SM than its own stores manage.  Two buffers
+      // alternate; a buffer is refilled once the store issued from it two
+      // blocks ago has read it.
+      auto store_rows = [&](const uint32_t* w, int c, int width) {
+        if (!tma_out || width != CHUNK) {
+          if (tma_out) {  // the plain path reuses the first buffer
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+          }
+          store_staged(w, c, width);
+          return;
+        }
+        const uint32_t buf = my_buf + (buf_use & 1) * EPI_BUF_BYTES;
+        if (buf_use >= 2) {
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        ++buf_use;
+        const uint32_t rowaddr = buf + lane * 128;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          st_shared_v4(rowaddr + ((u ^ (lane & 7)) << 4), w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&params.map_d, buf, col0 + c, row0);
+          tma_store_commit();
+        }
+      };
+
       // A 256-wide block-scaled tile leaves tensor memory no room for a second
       // accumulator, so the MMA warp idles until this one is handed back.  The
       // hand-back therefore comes as early as possible: the first two 64-column
@@ -703,12 +735,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           tmem_ld_32(acc_tmem + 64, vb), tmem_ld_32(acc_tmem + 96, vb + 32);
           pack64(va, held);
           before_global_memory();
-          store_staged(held, 0, 64);
+          store_rows(held, 0, 64);
           tmem_ld_wait();
           tmem_ld_settle_32(vb), tmem_ld_settle_32(vb + 32);
           tmem_ld_32(acc_tmem + 128, va), tmem_ld_32(acc_tmem + 160, va + 32);
           pack64(vb, held);
-          store_staged(held, 64, 64);
+          store_rows(held, 64, 64);
           tmem_ld_wait();
           tmem_ld_settle_32(va), tmem_ld_settle_32(va + 32);
           tmem_ld_32(acc_tmem + 192, vb), tmem_ld_32(acc_tmem + 224, vb + 32);
@@ -723,8 +755,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
             else mbar_arrive(bar_acc_empty + 8 * slot);
           }
           handed_back = true;
-          store_staged(held, 128, 64);
-          store_staged(held + 32, 192, 64);
+          store_rows(held, 128, 64);
+          store_rows(held + 32, 192, 64);
         }
       }
 
@@ -968,37 +1000,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_kernel(const __grid_constant_
           continue;
         }
 
-        if (tma_out && width == CHUNK && row0 < rows_m) {
-          // Long K loops hide the stores entirely, and a TMA store costs the
-          // fewest instructions (and the least power on a capped part): stage
-          // the 32 x 128-byte block, then one lane stores the box, which TMA
-          // clips at the edges of D.  Two buffers alternate.
+        if (staged && row0 < rows_m) {
           if constexpr (OUT_BYTES == 4) {
-            const uint32_t buf = my_buf + (buf_use & 1) * EPI_BUF_BYTES;
-            if (buf_use >= 2) {
-              if (lane == 0) tma_store_wait_read<1>();
-              __syncwarp();
-            }
-            ++buf_use;
-            const uint32_t rowaddr = buf + lane * 128;
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              st_shared_v4(rowaddr + ((u ^ (lane & 7)) << 4), v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&params.map_d, buf, col0 + c, row0);
-              tma_store_commit();
-            }
-          }
-        } else if (staged && row0 < rows_m) {
-          if constexpr (OUT_BYTES == 4) {
-            store_staged(v, c, width);
+            store_rows(v, c, width);
           } else {
             uint32_t w[32];
 #pragma unroll
             for (int u = 0; u < 32; ++u) w[u] = pack2(v[2 * u], v[2 * u + 1]);
-            store_staged(w, c, width);
+            store_rows(w, c, width);
           }
         } else if (!transpose_out) {
           if (row < rows_m) {

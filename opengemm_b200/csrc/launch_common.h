@@ -196,9 +196,12 @@ inline int fill_params(const Plan& p, const OgGemm& g, const LaunchPointers& io,
   if (rc != OG_OK) return rc;
   const bool c_aligned = (reinterpret_cast<uintptr_t>(io.c) & 15) == 0;
   const int epi_staged = p.epi_staged && c_aligned;
-  const int epi_tma = p.epi_tma && c_aligned;
+  const int epi_tma = p.epi_tma && c_aligned && !io.out_quant;  // block-scaled C is stored by its own path
   if (epi_tma) {
-    const int type = p.format->out == OUT_S32 ? int(CU_TENSOR_MAP_DATA_TYPE_INT32) : int(CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+    const int type = p.format->out == OUT_S32    ? int(CU_TENSOR_MAP_DATA_TYPE_INT32)
+                     : p.format->out == OUT_BF16 ? int(CU_TENSOR_MAP_DATA_TYPE_BFLOAT16)
+                     : p.format->out == OUT_F16  ? int(CU_TENSOR_MAP_DATA_TYPE_FLOAT16)
+                                                 : int(CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
     rc = encode_2d(&params.map_d, io.c, type, uint64_t(g.n), uint64_t(g.m), uint64_t(g.n) * p.out_bytes,
                    uint32_t(128 / p.out_bytes), 32, CU_TENSOR_MAP_SWIZZLE_128B, 0, "the output", why, why_cap);
     if (rc != OG_OK) return rc;

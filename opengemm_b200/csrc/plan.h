@@ -189,7 +189,7 @@ constexpr TileShape tile_shape(int smem_bits, int sf_block, int cta_group, int o
   }
   t.stage_bytes = (t.x_bytes + t.y_bytes + t.sf_bytes + 1023) / 1024 * 1024;
   t.epi_staged = epi >= 1 ? 1 : 0;
-  t.epi_tma = (epi == 2 && out_bytes == 4) ? 1 : 0;
+  t.epi_tma = epi == 2 ? 1 : 0;
   const int epi_bytes = (t.epi_staged ? 4 * (t.epi_tma ? 2 : 1) * (32 * 128) : 0) + (cluster_k - 1) * tile_n * 512;
   const int fit = (227 * 1024 - (1024 + 512) - epi_bytes) / t.stage_bytes;
   t.stages = fit < 16 ? fit : 16;
@@ -266,10 +266,18 @@ inline int make_plan(const OgGemm& g, int sm_count, Plan* out, char* why, size_t
   p.out_bytes = (f->out == OUT_BF16 || f->out == OUT_F16) ? 2 : 4;
   p.k_blocks = ceil_div(p.k, 1024 / smem_bits);
   const int64_t ldd = g.n;              // C is [m, n] row-major whichever way the MMA runs
-  // 32-bit output behind a long K loop leaves by TMA store (two buffers per
-  // warp); everything else staged leaves by plain stores (one buffer).
-  const bool staged = !g.epi_direct && !p.swap && (ldd * p.out_bytes) % 16 == 0;
-  const bool by_tma = staged && p.out_bytes == 4 && p.k_blocks >= 8 && p.tile_n % 32 == 0;
+  // Staged rows leave by TMA store (32 rows x 128 bytes a time, two buffers per
+  // warp) wherever a tile is whole 128-byte chunks wide: measured against plain
+  // 16-byte stores of the same staged rows it is level on a single tile and up
+  // to 1.3x faster where the stores are the work (bf16 8192x8192x32: 67.7 ->
+  // 52.8 us, 2048x2048x128: 6.9 -> 5.7 us).  16-bit output behind a long K loop
+  // keeps the plain stores: nothing waits for them there, and the second
+  // buffer would cost the widest block-scaled tiles a ring stage.
+  // epi_direct: 0 as above, 1 every thread stores its own row, 2 TMA stores
+  // for 16-bit output too, whatever the length of the K loop.
+  const bool staged = g.epi_direct != 1 && !p.swap && (ldd * p.out_bytes) % 16 == 0;
+  const bool by_tma = staged && (p.out_bytes == 4 ? p.tile_n % 32 == 0
+                                                  : p.tile_n % 64 == 0 && (p.k_blocks <= 16 || g.epi_direct == 2));
   p.epi = by_tma ? 2 : staged ? 1 : 0;
   // Cluster-K: the requested power of two, no more ways than there are K
   // blocks, halved until the landing zone leaves room for a three-stage ring.

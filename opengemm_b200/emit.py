@@ -29,7 +29,8 @@ from .log import log
 
 MARK = "// opengemm"
 CSRC = Path(__file__).resolve().parent / "csrc"
-OUT_TYPES = {0: "CU_TENSOR_MAP_DATA_TYPE_FLOAT32", 1: "CU_TENSOR_MAP_DATA_TYPE_INT32", 2: "CU_TENSOR_MAP_DATA_TYPE_BFLOAT16"}
+OUT_TYPES = {0: "CU_TENSOR_MAP_DATA_TYPE_FLOAT32", 1: "CU_TENSOR_MAP_DATA_TYPE_INT32", 2: "CU_TENSOR_MAP_DATA_TYPE_BFLOAT16",
+             3: "CU_TENSOR_MAP_DATA_TYPE_FLOAT16"}
 KIND_NAMES = ["KIND_F16", "KIND_TF32", "KIND_I8", "KIND_F8F6F4", "KIND_MXF8F6F4", "KIND_MXF4", "KIND_NVF4"]
 
 # Plan fields the kernel reads that are fixed by (dtype, shape, configuration).

@@ -116,6 +116,15 @@ def reference(entry, name):
 def runner(buffers, bound):
     """A zero-argument callable launching the bound kernel on the next rotation."""
     lib, g = bound
+    if hasattr(lib, "launcher"):  # addresses taken once per rotation, not once per call
+        cycle = itertools.cycle([(lib.launcher(g, r.a, r.b, r.sfa, r.sfb, r.out), r.out) for r in buffers])
+
+        def call():
+            launch, out = next(cycle)
+            launch()
+            return out
+
+        return call
     cycle = itertools.cycle(buffers)
 
     def call():

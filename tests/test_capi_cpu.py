@@ -136,7 +136,7 @@ def test_plan_invariants_over_the_shape_suite():
             assert p["tile_n"] % 16 == 0 and 16 <= p["tile_n"] <= 256
             assert p["num_tiles"] == p["tiles_m"] * p["tiles_n"] and 1 <= p["grid"] <= 148
             if p["epi_tma"]:
-                assert p["epi_staged"] and p["out_bytes"] == 4 and p["tile_n"] % 32 == 0
+                assert p["epi_staged"] and p["tile_n"] % (128 // p["out_bytes"]) == 0  # whole 128-byte chunks
             assert p["out_bytes"] == (2 if (name in NARROW_OUT or DTYPES[base_name(name)].out is torch.bfloat16) else 4)
             checked += 1
     assert checked > 1000

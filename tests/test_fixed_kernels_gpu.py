@@ -21,13 +21,14 @@ FIXED = [
     ("u8", dict(use_2cta=True, output_n=256), 1024),
     ("e4m3", dict(use_2cta=True, output_n=256), 1536),
     ("e2m1", dict(use_2cta=True, output_n=256), 1024),
-    ("e4m3xe5m2.bf16", dict(use_2cta=True, output_n=256), 1024),
-    ("nvfp4", dict(use_2cta=True, output_n=192), 1024),
-    ("nvfp4", dict(use_2cta=True, output_n=256), 1024),
-    ("mxfp4", dict(use_2cta=True, output_n=256), 1024),
-    ("mxfp4", dict(use_2cta=False, output_n=256), 2048),
-    ("mxfp8", dict(use_2cta=True, output_n=256), 1024),
-    ("mxfp8", dict(use_2cta=True, output_n=192), 1024),
+    # 16-bit output: more than 16 K blocks, below which the plan stores by TMA and no fixed-shape kernel does
+    ("e4m3xe5m2.bf16", dict(use_2cta=True, output_n=256), 2304),
+    ("nvfp4", dict(use_2cta=True, output_n=192), 4608),
+    ("nvfp4", dict(use_2cta=True, output_n=256), 4608),
+    ("mxfp4", dict(use_2cta=True, output_n=256), 4608),
+    ("mxfp4", dict(use_2cta=False, output_n=256), 4608),
+    ("mxfp8", dict(use_2cta=True, output_n=256), 2304),
+    ("mxfp8", dict(use_2cta=True, output_n=192), 2304),
 ]
 IDS = [f"{name}-{'pair' if knobs['use_2cta'] else 'single'}-{knobs['output_n']}" for name, knobs, _ in FIXED]
 
