@@ -14,15 +14,15 @@ from . import capi
 from .configs import resolve_config
 from .dtypes import DTYPES, NARROW_OUT, NARROW_OUT_SUFFIXES, base_name, dtype_name, extent, k_of, lookup, sf_block
 
-_bound = {}  # (dtype name, m, n, k) -> (Library, OgGemm), for the life of the process
+_bound = {}  # (dtype name, m, n, k, launch mode) -> (Library, OgGemm), for the life of the process
 
 
 def bind(name, m, n, k, device):
-    """Resolve and memoise the kernel for a shape."""
+    """Resolve and memoise the kernel for a shape in the library's current launch mode."""
     with torch.cuda.device(device):
         config = resolve_config(base_name(name), m, n, k)  # the bf16-output variant runs its format's tile plan
-    _bound[(name, m, n, k)] = capi.bind(name, m, n, k, config)
-    return _bound[(name, m, n, k)]
+    _bound[(name, m, n, k, capi.independent_inputs())] = capi.bind(name, m, n, k, config)
+    return _bound[(name, m, n, k, capi.independent_inputs())]
 
 
 def forget(name=None):
@@ -123,7 +123,7 @@ def gemm(a, b, sfa=None, sfb=None, out=None, atype=None, btype=None, out_dtype=N
     d = lookup(name)
     m, n, k = a.size(0), b.size(0), k_of(d, a.size(1))
     check_operands(d, m, n, k, a, b, sfa, sfb)
-    lib, g = _bound.get((name, m, n, k)) or bind(name, m, n, k, a.device)
+    lib, g = _bound.get((name, m, n, k, capi.independent_inputs())) or bind(name, m, n, k, a.device)
     out = output(d, m, n, out, a.device)
     if alpha is None and bias is None:
         lib.launch(g, a, b, sfa, sfb, out)

@@ -79,8 +79,10 @@ def measure(name, m, n, k, window_ms, tune_missing=False, cutlass=None):
         except RuntimeError as exc:
             row["status"] = f"skipped: {str(exc)[:100]}"
             return row
-    config = stored["config"] if stored else configs.heuristic_config(name, m, n, k)
+    dependent = not configs.independent_mode()
+    config = configs.config_of(stored, dependent) if stored else configs.resolve_config(name, m, n, k, dependent)
     row["source"] = "stored" if stored else "heuristic"
+    row["launches"] = "dependent" if dependent else "independent"
     try:
         bound = capi.bind(name, m, n, k, config)
     except RuntimeError as exc:

@@ -354,6 +354,11 @@ _libraries, _lock = {}, threading.Lock()
 _independent_inputs = False  # mirror of the library's process-wide switch
 
 
+def independent_inputs():
+    """The setting `Library.set_independent_inputs` last made in this process (default off)."""
+    return _independent_inputs
+
+
 def library(impl):
     """The loaded library for `impl`, loading it on first use."""
     with _lock:

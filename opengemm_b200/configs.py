@@ -10,6 +10,19 @@ rename.  Files written by the reference load unchanged.
 Where the reference tunes on the spot when nothing is stored
 (configs.py:63-80), this build answers from `heuristic_config` unless
 OPENGEMM_AUTOTUNE=1 asks for a sweep, so an untuned shape costs no GPU minutes.
+
+One addition to the schema: an entry may carry `config_dependent` (and
+`measured_dependent`) beside `config`.  The reference's kernels never wait for
+the previous kernel of the stream before they load (its launches always
+overlap, opengemm/src/mm/kernel.cuh:209,479-483), so its one configuration per
+shape is the best for back-to-back launches of independent GEMMs.  Here that
+is a mode the caller opts into (`og_b200_set_independent_inputs`); by default
+a launch's loads wait for the previous kernel, as a chain of dependent GEMMs
+needs.  The two modes want different plans wherever a GEMM has fewer tiles
+than the GPU has SMs: independent launches run side by side, so a few fat CTAs
+win; a dependent launch has the GPU to itself and wants every SM it can use.
+`config` is the former (what the reference's schema means), `config_dependent`
+the latter, stored only where tuning found it to differ.
 """
 
 import json
@@ -177,16 +190,18 @@ def modelled_us(name, m, n, k, use_2cta, output_n, swap_ab):
     return max(path_us, power_us, hbm_us) + store / (BOOST_GHZ * 1e3)
 
 
-def heuristic_config(name, m, n, k):
+def heuristic_config(name, m, n, k, dependent=False):
     """A configuration chosen by rule, for shapes nothing is stored for.
 
     Small M rides the MMA's N side (swap_ab) so the 128-row side streams B.
     Pair size and tile width minimise `modelled_us`; estimates within 2 %
-    go to the pair and the wider tile (less operand traffic).
+    go to the pair and the wider tile (less operand traffic).  `dependent`:
+    for launches that wait for the previous kernel (the default mode), where
+    nothing is gained by leaving SMs to the neighbouring launches.
     """
     d = DTYPES[name]
     scaled = d.impl == "smm"
-    if scaled and d.bits == 4 and m <= 64 and n >= 1024:
+    if scaled and d.bits == 4 and m <= 64 and n >= 1024 and not dependent:
         # Block-scaled fp4 decode (tuned on 1..64 x 7168..57344 x 8192): 128 x 256 tiles
         # on single CTAs, M on the padded 128-row side (rows past M are TMA zero fill and
         # cost no traffic).  Few fat CTAs let consecutive launches run side by side.
@@ -216,7 +231,8 @@ def heuristic_config(name, m, n, k):
             # for one accumulator only, loses a little more than the model's drain term
             # says (192 won 9 of 12 tuned large block-scaled shapes).
             ctas = -(-rows_m // (256 if two else 128)) * -(-rows_n // width) * (2 if two else 1)
-            cost = max(cost, LAUNCH_FLOOR_US) + CTA_US * min(ctas, SM_COUNT)
+            if not dependent:
+                cost = max(cost, LAUNCH_FLOOR_US) + CTA_US * min(ctas, SM_COUNT)
             if scaled and two and width == 256:
                 cost *= 1.08
             if two and cost < PAIR_FROM_US:
@@ -249,29 +265,46 @@ def _with_defaults(knobs, scaled):
     return config
 
 
-def resolve_config(name, m, n, k):
+def independent_mode():
+    """Whether this process has told the library that launches' inputs are independent."""
+    from . import capi
+
+    return capi.independent_inputs()
+
+
+def config_of(entry, dependent):
+    """The configuration of a stored entry for the launch mode."""
+    if dependent and entry.get("config_dependent") is not None:
+        return entry["config_dependent"]
+    return entry["config"]
+
+
+def resolve_config(name, m, n, k, dependent=None):
     """The configuration for a (dtype, shape): stored, else tuned now when
     OPENGEMM_AUTOTUNE=1, else what is stored for a format of the same kernel
-    family (`KERNEL_FAMILIES`), else the heuristic.
+    family (`KERNEL_FAMILIES`), else the heuristic.  `dependent` picks between
+    an entry's two configurations (default: by the library's current mode).
 
     Raises:
         ValueError: if the shape is recorded as unimplementable.
     """
+    if dependent is None:
+        dependent = not independent_mode()
     entry = stored_entry(name, m, n, k)
     if entry is None:
         if os.environ.get("OPENGEMM_AUTOTUNE") == "1":
             from .tune import tune
 
             log(f"no stored configuration for {name} {m}x{n}x{k}; tuning it now")
-            return tune(name, m, n, k)
+            return tune(name, m, n, k, dependent=dependent)
         entry = sibling_entry(name, m, n, k)
         if entry is not None:
-            return entry["config"]
-        return heuristic_config(name, m, n, k)
+            return config_of(entry, dependent)
+        return heuristic_config(name, m, n, k, dependent)
     if entry.get("config") is None:
         why = entry.get("unimplementable", "recorded as unimplementable")
         raise ValueError(f"{name} {m}x{n}x{k} cannot be served: {why}")
-    return entry["config"]
+    return config_of(entry, dependent)
 
 
 def write_entry(impl, entry):

@@ -25,7 +25,7 @@ import argparse
 import torch
 
 from . import capi, harness
-from .configs import heuristic_config, load_shapes, write_entry
+from .configs import heuristic_config, load_shapes, stored_entry, write_entry
 from .dtypes import DTYPES
 from .log import log
 
@@ -106,8 +106,13 @@ def label(config):
     return text
 
 
-def tune(name, m, n, k, verbose=False, window_ms=15.0, final_ms=60.0):
+def tune(name, m, n, k, verbose=False, window_ms=15.0, final_ms=60.0, dependent=False):
     """Sweep one (dtype, shape), store the winner and return its configuration.
+
+    `dependent` times the candidates as launches that wait for the previous
+    kernel of the stream (the library's default mode) and stores the winner as
+    the entry's `config_dependent`, beside whatever `config` it already has;
+    otherwise as launches of independent GEMMs, which may overlap, into `config`.
 
     Raises:
         RuntimeError: if no candidate is correct, or the format cannot take this K.
@@ -115,14 +120,14 @@ def tune(name, m, n, k, verbose=False, window_ms=15.0, final_ms=60.0):
     impl = DTYPES[name].impl
     library = capi.library(impl)
     # the operand sets below are written once, before any launch; the caller's setting comes back at the end
-    independent_before = library.set_independent_inputs(True)
+    independent_before = library.set_independent_inputs(not dependent)
     try:
-        return _tune(name, m, n, k, impl, library, verbose, window_ms, final_ms)
+        return _tune(name, m, n, k, impl, library, verbose, window_ms, final_ms, dependent)
     finally:
         library.set_independent_inputs(independent_before)
 
 
-def _tune(name, m, n, k, impl, library, verbose, window_ms, final_ms):
+def _tune(name, m, n, k, impl, library, verbose, window_ms, final_ms, dependent):
     buffers = harness.make_input_set(m, n, k, name)
     want = harness.reference(buffers[0], name)
     space = geometry_candidates(name, m, n, k)
@@ -178,7 +183,13 @@ def _tune(name, m, n, k, impl, library, verbose, window_ms, final_ms):
     base = harness.timed(baseline, window_ms=final_ms, repeats=3) if baseline else None
     log(f"best: {label(best)}  ({len(ranked)} timed, {rejected} failed correctness)")
     measured = {"us": round(us, 3), "cublas_us": base and round(base, 3), "env": harness.env_stamp()}
-    path = write_entry(impl, {"dtype": name, "m": m, "n": n, "k": k, "config": best, "measured": measured})
+    entry = dict(stored_entry(name, m, n, k) or {"dtype": name, "m": m, "n": n, "k": k})
+    if dependent:
+        entry.update(config_dependent=best, measured_dependent=measured)
+        entry.setdefault("config", best)  # the schema's one mandatory configuration
+    else:
+        entry.update(config=best, measured=measured)
+    path = write_entry(impl, entry)
     if base:
         log(f"kernel {us:.2f}us  cuBLAS {base:.2f}us  {base / us:.3f}x; stored in {path}")
     else:
@@ -196,12 +207,15 @@ def main():
     group.add_argument("--shape", nargs=3, type=int, metavar=("M", "N", "K"))
     group.add_argument("--all", action="store_true", help="every shape in shapes.jsonc")
     parser.add_argument("--verbose", action="store_true")
+    parser.add_argument("--dependent", action="store_true",
+                        help="tune for launches that wait for the previous kernel (stored as config_dependent)")
     parser.add_argument("--window-ms", type=float, default=15.0, help="timing window of the sweep")
     parser.add_argument("--final-ms", type=float, default=60.0, help="timing window of the closing round among the leaders")
     args = parser.parse_args()
     for m, n, k in [tuple(args.shape)] if args.shape else load_shapes():
         try:
-            tune(args.dtype, m, n, k, verbose=args.verbose, window_ms=args.window_ms, final_ms=args.final_ms)
+            tune(args.dtype, m, n, k, verbose=args.verbose, window_ms=args.window_ms, final_ms=args.final_ms,
+                 dependent=args.dependent)
         except RuntimeError as exc:
             print(exc, flush=True)
 

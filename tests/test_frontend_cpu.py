@@ -76,8 +76,9 @@ def test_torch_quant_helpers_match_reference_fixtures(golden_dir):
 def test_config_store_round_trip(tmp_path, monkeypatch):
     monkeypatch.setenv("OPENGEMM_CONFIGS", str(tmp_path))
     assert configs.stored_entry("bf16", 96, 96, 96) is None
-    cfg = configs.resolve_config("bf16", 96, 96, 96)  # nothing stored: the heuristic answers
-    assert cfg == configs.heuristic_config("bf16", 96, 96, 96)
+    cfg = configs.resolve_config("bf16", 96, 96, 96)  # nothing stored: the heuristic answers, for dependent launches by default
+    assert cfg == configs.heuristic_config("bf16", 96, 96, 96, dependent=True)
+    assert configs.resolve_config("bf16", 96, 96, 96, dependent=False) == configs.heuristic_config("bf16", 96, 96, 96)
     entry = {"dtype": "bf16", "m": 96, "n": 96, "k": 96, "config": dict(cfg, output_n=32)}
     path = configs.write_entry("mm", entry)
     assert path == tmp_path / "tuned_configs.json"
@@ -99,10 +100,27 @@ def test_a_format_without_an_entry_takes_its_kernel_familys(tmp_path, monkeypatc
     configs.write_entry("mm", {"dtype": "e4m3", "m": shape[0], "n": shape[1], "k": shape[2], "config": odd})
     for name in ("e5m2", "e2m1", "e4m3xe5m2"):
         assert configs.resolve_config(name, *shape) == odd
-    assert configs.resolve_config("bf16", *shape) == configs.heuristic_config("bf16", *shape)  # another kernel
+    assert configs.resolve_config("bf16", *shape) == configs.heuristic_config("bf16", *shape, dependent=True)  # another kernel
     own = dict(odd, output_n=96)
     configs.write_entry("mm", {"dtype": "e5m2", "m": shape[0], "n": shape[1], "k": shape[2], "config": own})
     assert configs.resolve_config("e5m2", *shape) == own  # its own entry wins
+
+
+def test_an_entry_may_hold_one_configuration_per_launch_mode(tmp_path, monkeypatch):
+    monkeypatch.setenv("OPENGEMM_CONFIGS", str(tmp_path))
+    shape = (64, 7168, 8192)
+    fat = dict(configs.heuristic_config("mxfp4", *shape), output_n=256)
+    wide = dict(fat, output_n=64)
+    configs.write_entry("smm", {"dtype": "mxfp4", "m": shape[0], "n": shape[1], "k": shape[2], "config": fat})
+    assert configs.resolve_config("mxfp4", *shape) == fat  # one configuration serves both modes
+    configs.write_entry("smm", {"dtype": "mxfp4", "m": shape[0], "n": shape[1], "k": shape[2], "config": fat,
+                                "config_dependent": wide})
+    assert configs.resolve_config("mxfp4", *shape, dependent=True) == wide
+    assert configs.resolve_config("mxfp4", *shape, dependent=False) == fat
+    assert configs.resolve_config("mxfp4", *shape) == wide  # the library's default mode is the dependent one
+    # the heuristic spreads a dependent decode launch over more CTAs than an independent one
+    a, b = configs.heuristic_config("mxfp4", 64, 7000, 8192), configs.heuristic_config("mxfp4", 64, 7000, 8192, dependent=True)
+    assert a["output_n"] >= b["output_n"]
 
 
 def test_config_store_reads_a_file_in_the_references_schema(tmp_path, monkeypatch, golden_dir):
