@@ -636,7 +636,7 @@ def reference_kernel_leg(torch, r, unit):
     if found is None:
         return {"unavailable": "the reference's kernel libraries are not built under oracle/_ref"}
     sets = [(ops.a, ops.b, ops.sfa, ops.sfb, out) for ops, out in r.sets]
-    result = compare.interleaved(found, r.name, r.m, r.n, r.k, sets, ours=(r.lib, r.g), windows=4, window_ms=60.0)
+    result = compare.interleaved(found, r.name, r.m, r.n, r.k, sets, ours=(r.lib, r.g), windows=8, window_ms=60.0)
     if "ref_us" in result:
         result["ref_rate"] = round(r.rate(result["ref_us"], unit), 1)
         result["ours_rate"] = round(r.rate(result["ours_us"], unit), 1)

@@ -96,6 +96,25 @@ def test_all_shipped_reference_knob_sets_bind(golden_dir):
             assert lib.plan(g)["tiles"] >= 1
 
 
+def test_every_shipped_configuration_binds():
+    """Both configurations of every entry of the shipped store (one per launch
+    mode where tuning found two) bind, and carry the measurement they came from."""
+    from opengemm_b200 import configs
+
+    total = second = 0
+    for impl in ("mm", "smm"):
+        lib = capi.library(impl)
+        for e in json.loads(configs.config_path(impl).read_text())["entries"]:
+            total += 1
+            assert lib.plan(lib.bind(e["dtype"], e["m"], e["n"], e["k"], e["config"]))["tiles"] >= 1
+            assert e["measured"]["us"] > 0
+            if e.get("config_dependent") is not None:
+                second += 1
+                assert e["config_dependent"] != e["config"] and e["measured_dependent"]["us"] > 0
+                assert lib.plan(lib.bind(e["dtype"], e["m"], e["n"], e["k"], e["config_dependent"]))["tiles"] >= 1
+    assert total >= 400 and second >= 100
+
+
 def test_plan_of_the_baseline_configurations():
     for name, m, n, k in [("bf16", 1024, 1024, 1024), ("e4m3", 4096, 4096, 4096), ("s8", 8192, 8192, 8192),
                           ("s8", 8192, 1024, 8192), ("nvfp4", 8192, 28672, 8192), ("nvfp4", 8192, 3584, 8192),
