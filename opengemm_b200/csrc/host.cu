@@ -284,8 +284,31 @@ struct PlanMemo {
   OgGemm key;
   Plan plan;
   bool valid = false;
+  unsigned generation = 0;  // changes whenever `plan` does
 };
 thread_local PlanMemo plan_memo;
+
+// A launch's parameter block is a function of the bound GEMM, the caller's
+// pointers and the wait limit.  Loops that run the same buffers again and
+// again (serving, benchmarks) find theirs here and skip the pointer checks,
+// the tensor-map look-ups and the fill: per thread, sixteen blocks indexed by
+// a hash of the output address.
+struct ParamsMemo {
+  bool valid = false;
+  unsigned generation = 0;
+  LaunchPointers io{};
+  int* status = nullptr;
+  bool scaled_out = false;
+  float alpha = 1.0f;
+  unsigned long long wait_limit = 0;
+  GemmParams params;
+  bool matches(unsigned gen, const LaunchPointers& o, int* status_word, const float* a, unsigned long long limit) const {
+    return valid && generation == gen && io.a == o.a && io.b == o.b && io.sfa == o.sfa && io.sfb == o.sfb &&
+           io.c == o.c && io.bias == o.bias && io.out_quant == o.out_quant && io.c_scales == o.c_scales &&
+           status == status_word && scaled_out == (a != nullptr) && (!a || alpha == *a) && wait_limit == limit;
+  }
+};
+thread_local ParamsMemo params_memo[16];
 
 int launch_impl(const OgGemm* g, const LaunchPointers& io, int device, void* stream, int* status_word,
                 int want_scaled, const float* alpha = nullptr) {
@@ -297,21 +320,34 @@ int launch_impl(const OgGemm* g, const LaunchPointers& io, int device, void* str
     if (planned != OG_OK) return fail(planned, "%s", why);
     plan_memo.key = *g;
     plan_memo.valid = true;
+    ++plan_memo.generation;
   }
   const Plan& p = plan_memo.plan;
   char why[320];
   if (want_scaled >= 0 && int(p.format->scaled) != want_scaled)
     return fail(OG_ERR_LAUNCH, "dtype %.16s does not belong to this library", g->dtype);
-  int rc = check_pointers(*g, p, io, alpha, why, sizeof why);
-  if (rc != OG_OK) return fail(rc, "%s", why);
+  const unsigned long long wait_limit = current_wait_limit_ns();
+  ParamsMemo& memo = params_memo[(uint32_t(reinterpret_cast<uintptr_t>(io.c) >> 9) * 0x9E3779B1u) >> 28];
+  const bool remembered = memo.matches(plan_memo.generation, io, status_word, alpha, wait_limit);
+  if (!remembered) {
+    const int rc = check_pointers(*g, p, io, alpha, why, sizeof why);
+    if (rc != OG_OK) return fail(rc, "%s", why);
+  }
   const int followed = follow_device(device);
   if (followed != OG_OK) return followed;
   const int configured = ensure_configured(device, p.variant, p.smem_bytes);
   if (configured != OG_OK) return configured;
 
   GemmParams params;
-  rc = fill_params(p, *g, io, status_word, alpha, current_wait_limit_ns(), &params, why, sizeof why);
-  if (rc != OG_OK) return fail(rc, "%s", why);
+  if (remembered) {
+    params = memo.params;
+  } else {
+    const int rc = fill_params(p, *g, io, status_word, alpha, wait_limit, &params, why, sizeof why);
+    if (rc != OG_OK) return fail(rc, "%s", why);
+    memo.valid = true, memo.generation = plan_memo.generation, memo.io = io, memo.status = status_word;
+    memo.scaled_out = alpha != nullptr, memo.alpha = alpha ? *alpha : 1.0f, memo.wait_limit = wait_limit;
+    memo.params = params;
+  }
   if (overcredit_next) {  // testing aid: the stage barriers will wait for bytes that never come
     params.tx_bytes += overcredit_next;
     overcredit_next = 0;
