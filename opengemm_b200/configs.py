@@ -206,6 +206,11 @@ def heuristic_config(name, m, n, k, dependent=False):
         # on single CTAs, M on the padded 128-row side (rows past M are TMA zero fill and
         # cost no traffic).  Few fat CTAs let consecutive launches run side by side.
         return _with_defaults({"use_2cta": False, "output_n": 256, "swap_ab": False, "supergroup": 1}, scaled)
+    if scaled and m <= 64 and n >= 1024 and dependent:
+        # A block-scaled decode launch with the GPU to itself (tuned on 1..64 x 2048..14336):
+        # M on the padded 128-row side again, tiles narrow enough to put a CTA on most SMs.
+        width = 64 if n < 11264 else 128 if n < 28672 else 256
+        return _with_defaults({"use_2cta": False, "output_n": width, "swap_ab": False, "supergroup": 8}, scaled)
     swap = m <= 64 and n >= 2 * m
     rows_m, rows_n = (n, m) if swap else (m, n)
     # Widths that fill whole 128-byte lines of the staged rows.
@@ -272,11 +277,30 @@ def independent_mode():
     return capi.independent_inputs()
 
 
+def planned_ctas(config, m, n):
+    """CTAs a configuration launches for an M x N output (at most one per SM)."""
+    rows_m, rows_n = (n, m) if config.get("swap_ab") else (m, n)
+    pair = 2 if config.get("use_2cta") else 1
+    return min(SM_COUNT, -(-rows_m // (128 * pair)) * -(-rows_n // max(16, int(config["output_n"]))) * pair)
+
+
 def config_of(entry, dependent):
-    """The configuration of a stored entry for the launch mode."""
+    """The configuration of a stored entry for the launch mode.  An entry tuned
+    only for overlapping launches whose plan leaves most of the GPU idle is
+    passed over, for a dependent launch, when the rule for dependent launches
+    would put a third as many CTAs again to work (on the shapes tuned both ways
+    that rule chose at least 0.6 of the tuned CTA count every time)."""
     if dependent and entry.get("config_dependent") is not None:
         return entry["config_dependent"]
-    return entry["config"]
+    config = entry["config"]
+    if dependent and config is not None:
+        m, n = entry["m"], entry["n"]
+        used = planned_ctas(config, m, n)
+        if used < 100:
+            ruled = heuristic_config(entry["dtype"], m, n, entry["k"], dependent=True)
+            if planned_ctas(ruled, m, n) >= max(16, 1.3 * used):  # a handful of CTAs either way: launch-bound, leave it
+                return ruled
+    return config
 
 
 def resolve_config(name, m, n, k, dependent=None):

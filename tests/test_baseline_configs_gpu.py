@@ -55,20 +55,29 @@ def test_baseline_configuration_matches_the_oracle(key, ways):
                              None if ops.sfb_raw is None else ops.sfb_raw[n0:n1])
     if name == "s8":
         assert int(ops.a.min()) == -128 and int(ops.b.min()) == -128  # the full range, -128 x -128 included
-    lib, g = capi.bind(name, m, n, k, configs.resolve_config(name, m, n, k))
-    out = torch.empty((m, n), device="cuda", dtype=d.out)
-    out.view(torch.uint8).fill_(0x7F)
-    lib.set_wait_limit_ms(2000)
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    lib.launch_checked(g, ops.a, ops.b, ops.sfa, ops.sfb, out, status)
-    torch.cuda.synchronize()
-    assert int(status.item()) == 0, f"device wait gave up: {int(status.item())} ({lib.plan(g)})"
-    result = bench.sampled_oracle_check(torch, name, k, ops, out)
-    print(f"{key} {m}x{n}x{k} {name}: {result}")
-    assert result["ok"], result
-    if d.out is torch.int32:
-        assert result["max_rel"] == 0.0
-    del out
+    # The store may hold one configuration per launch mode (overlapping launches of
+    # independent GEMMs, what bench.py times; dependent launches, the library's default):
+    # both are what gemm() would run, so both are checked where they differ.
+    tried = []
+    for dependent in (False, True):
+        config = configs.resolve_config(name, m, n, k, dependent=dependent)
+        if config in tried:
+            continue
+        tried.append(config)
+        lib, g = capi.bind(name, m, n, k, config)
+        out = torch.empty((m, n), device="cuda", dtype=d.out)
+        out.view(torch.uint8).fill_(0x7F)
+        lib.set_wait_limit_ms(2000)
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        lib.launch_checked(g, ops.a, ops.b, ops.sfa, ops.sfb, out, status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, f"device wait gave up: {int(status.item())} ({lib.plan(g)})"
+        result = bench.sampled_oracle_check(torch, name, k, ops, out)
+        print(f"{key} {m}x{n}x{k} {name} ({'dependent' if dependent else 'independent'} launches): {result}")
+        assert result["ok"], result
+        if d.out is torch.int32:
+            assert result["max_rel"] == 0.0
+        del out
 
 
 def test_c3_full_output_has_no_sentinel_left():

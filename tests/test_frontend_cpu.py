@@ -112,7 +112,13 @@ def test_an_entry_may_hold_one_configuration_per_launch_mode(tmp_path, monkeypat
     fat = dict(configs.heuristic_config("mxfp4", *shape), output_n=256)
     wide = dict(fat, output_n=64)
     configs.write_entry("smm", {"dtype": "mxfp4", "m": shape[0], "n": shape[1], "k": shape[2], "config": fat})
-    assert configs.resolve_config("mxfp4", *shape) == fat  # one configuration serves both modes
+    assert configs.resolve_config("mxfp4", *shape, dependent=False) == fat
+    # tuned for overlapping launches only, on 28 of 148 SMs: a dependent launch takes the rule's plan instead
+    spread = configs.resolve_config("mxfp4", *shape)
+    assert configs.planned_ctas(fat, 64, 7168) == 28 and configs.planned_ctas(spread, 64, 7168) >= 100
+    full = dict(fat, output_n=32)  # an entry that already covers the GPU serves both modes
+    configs.write_entry("smm", {"dtype": "mxfp4", "m": 64, "n": 8192, "k": 4096, "config": full})
+    assert configs.resolve_config("mxfp4", 64, 8192, 4096) == full
     configs.write_entry("smm", {"dtype": "mxfp4", "m": shape[0], "n": shape[1], "k": shape[2], "config": fat,
                                 "config_dependent": wide})
     assert configs.resolve_config("mxfp4", *shape, dependent=True) == wide
