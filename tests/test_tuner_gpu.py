@@ -35,7 +35,13 @@ def test_tune_writes_a_correct_entry_that_gemm_then_resolves(name, shape, tmp_pa
     assert entry["config"] == best and entry["measured"]["us"] > 0 and "gpu" in entry["measured"]["env"]
     impl = og.DTYPES[name].impl
     assert set(capi.KERNEL_KEYS[impl]) <= set(best) | {"block_m", "epi_hold", "epi_double"}  # the schema's kernel keys
-    assert configs.resolve_config(name, m, n, k) == best
+    assert configs.resolve_config(name, m, n, k, dependent=False) == best
+    # the same shape tuned for launches that wait for their predecessor lands beside it
+    serial = tune.tune(name, m, n, k, window_ms=2.0, final_ms=4.0, dependent=True)
+    entry = json.loads((tmp_path / configs.TUNED_FILE).read_text())["entries"][0]
+    assert entry["config"] == best and entry["config_dependent"] == serial and entry["measured_dependent"]["us"] > 0
+    assert configs.resolve_config(name, m, n, k) == serial  # the library's default mode
+    assert not capi.independent_inputs()  # the tuner put the caller's mode back
     # the stored entry is what a bound GEMM now runs, and it is correct
     from opengemm_b200 import harness
 
