@@ -136,7 +136,7 @@ def _round_up(x, to):
 # costs less than its share of tiles suggests.
 LOAD_BYTES_PER_CLOCK = 80.0
 STORE_BYTES_PER_CLOCK = 27.0
-DRAIN_CLOCKS = 300.0    # single-accumulator tiles: the MMA warp waits while tensor memory is read out
+DRAIN_CLOCKS = 2000.0   # single-accumulator tiles: the MMA warp waits while tensor memory is read out
 TILE_CLOCKS = 1200.0    # hand-offs per tile that nothing overlaps
 PAIR_CLOCKS = 400.0     # more of them when two CTAs share a tile (barriers across the pair)
 TRAFFIC_ENERGY = 0.25   # energy of moving a clock's worth of operand bytes, in tensor-pipe clocks
@@ -156,11 +156,15 @@ def _smem_bytes_per_value(name):
     return max(1.0, d.bits / 8)  # dense sub-byte values are unpacked to bytes by the tensor map
 
 
-def modelled_us(name, m, n, k, use_2cta, output_n, swap_ab):
+def modelled_us(name, m, n, k, use_2cta, output_n, swap_ab, dependent=False):
     """Estimated microseconds for one GEMM with the given tiling: the slower
     of the critical path (waves x tile time at the boost clock, the K loop
     bound by the tensor pipe or by L2 -> shared-memory traffic) and the
-    power-limited time of all tiles' work spread over the SMs."""
+    power-limited time of all tiles' work spread over the SMs.  `dependent`:
+    the launch does not overlap its neighbours, so a long kernel's waves run
+    at the power-limited clock one after the other (a partly filled last wave
+    then costs a whole tile time: mxfp8 2048x2048x14336 on 88 tiles of 256x192
+    takes 49 us per launch overlapping and 74 us alone)."""
     d = DTYPES[name]
     scaled = d.impl == "smm"
     rows_m, rows_n = (n, m) if swap_ab else (m, n)
@@ -180,8 +184,8 @@ def modelled_us(name, m, n, k, use_2cta, output_n, swap_ab):
     extra = TILE_CLOCKS + (PAIR_CLOCKS if use_2cta else 0.0) + (DRAIN_CLOCKS if scaled and output_n > 192 else 0.0)
     tile = max(k_blocks * max(compute, load), store) + extra
     energy = max(k_blocks * (compute + TRAFFIC_ENERGY * load), store) + extra
-    path_us = waves * tile / (BOOST_GHZ * 1e3)
     power_us = tiles / slots * energy / (CAPPED_GHZ * 1e3)
+    path_us = waves * tile / ((CAPPED_GHZ if dependent and power_us > 15.0 else BOOST_GHZ) * 1e3)
     # Operands and output cross HBM at least once; few CTAs cannot keep enough
     # loads in flight to saturate it.
     hbm_bytes = (m * k + n * k) * d.bits / 8 + m * n * d.out.itemsize
@@ -229,17 +233,14 @@ def heuristic_config(name, m, n, k, dependent=False):
         for width in reversed(widths):
             if two and width < 32:
                 continue
-            cost = modelled_us(name, m, n, k, two, width, swap)
-            # Measured corrections to the model: a launch is never shorter than the
-            # launch floor, below which fewer CTAs win (consecutive launches then run
-            # side by side); a 256-wide block-scaled pair tile, which has tensor memory
-            # for one accumulator only, loses a little more than the model's drain term
-            # says (192 won 9 of 12 tuned large block-scaled shapes).
+            cost = modelled_us(name, m, n, k, two, width, swap, dependent)
+            # Measured corrections to the model: an overlapping launch is never shorter
+            # than the launch floor, below which fewer CTAs win (consecutive launches
+            # then run side by side); a short kernel loses about a microsecond to a
+            # pair's set-up.
             ctas = -(-rows_m // (256 if two else 128)) * -(-rows_n // width) * (2 if two else 1)
             if not dependent:
                 cost = max(cost, LAUNCH_FLOOR_US) + CTA_US * min(ctas, SM_COUNT)
-            if scaled and two and width == 256:
-                cost *= 1.08
             if two and cost < PAIR_FROM_US:
                 cost += PAIR_SETUP_US  # single CTAs won 90 % of the tuned shapes that run under 9 us
             if best is None or cost < best[0] * 0.98:
