@@ -280,3 +280,19 @@ def test_build_staleness_is_by_content_and_the_cache_follows_the_environment(tmp
     assert build.library_path("mm") == expected
     monkeypatch.setenv("OPENGEMM_LIB_MM", "/somewhere/else.so")
     assert str(build.library_path("mm")) == "/somewhere/else.so"
+
+
+def test_heuristic_makes_the_tuned_pair_or_single_choice_on_most_shipped_entries():
+    """A guard on the rule that serves untuned shapes: against what tuning found,
+    per launch mode, over the whole shipped store."""
+    for dependent, key in ((False, "config"), (True, "config_dependent")):
+        same = total = 0
+        for impl in ("mm", "smm"):
+            for e in json.loads(configs.config_path(impl).read_text())["entries"]:
+                tuned = e.get(key)
+                if tuned is None:
+                    continue
+                ruled = configs.heuristic_config(e["dtype"], e["m"], e["n"], e["k"], dependent=dependent)
+                same += bool(ruled["use_2cta"]) == bool(tuned["use_2cta"])
+                total += 1
+        assert total >= 300 and same >= 0.8 * total, (dependent, same, total)
