@@ -57,17 +57,22 @@ struct MapKey {
 struct MapSlot {
   MapKey key{};
   CUtensorMap map;
-  bool used = false;
 };
 
 // 64 sets of four ways: a loop over a few rotating operand sets keeps a dozen
 // or two maps alive, and in a direct-mapped table two of those would often
 // share a slot and evict each other on every call (a driver call each time).
+// A set's four hash tags sit together in half a cache line and are all a
+// miss reads: a loop over more buffers than the table holds (benchmarks that
+// rotate hundreds of operand sets past L2) then pays one line per look-up
+// instead of four keys spread over a dozen lines it has not touched since the
+// table last wrapped.
 constexpr int MAP_SETS = 64;
 constexpr int MAP_WAYS = 4;
 struct MapSet {
+  uint64_t tag[MAP_WAYS] = {0, 0, 0, 0};  // the slot's full hash with bit 0 set; 0 = empty
+  unsigned next = 0;                      // the way the next miss replaces
   MapSlot way[MAP_WAYS];
-  unsigned next = 0;  // the way the next miss replaces
 };
 inline thread_local MapSet map_cache[MAP_SETS];
 
@@ -87,13 +92,15 @@ inline int encode_2d(CUtensorMap* out, const void* base, int type, uint64_t dim0
   h = mix_hash(h, dim0 * 1315423911ull + dim1);
   h = mix_hash(h, (uint64_t(box0) << 32) | box1);
   h = mix_hash(h, stride * 31 + uint64_t(type) * 7 + uint64_t(swizzle) * 3 + uint64_t(l2));
-  MapSet& set = map_cache[h % MAP_SETS];
-  for (MapSlot& candidate : set.way)
-    if (candidate.used && candidate.key == key) {
-      *out = candidate.map;
+  MapSet& set = map_cache[(h >> 8) % MAP_SETS];
+  const uint64_t tag = h | 1;
+  for (int w = 0; w < MAP_WAYS; ++w)
+    if (set.tag[w] == tag && set.way[w].key == key) {
+      *out = set.way[w].map;
       return OG_OK;
     }
-  MapSlot& slot = set.way[set.next++ % MAP_WAYS];
+  const unsigned victim = set.next++ % MAP_WAYS;
+  MapSlot& slot = set.way[victim];
   EncodeFn encode = tensor_map_encoder();
   if (!encode) {
     snprintf(why, why_cap, "cuTensorMapEncodeTiled is not available: no CUDA driver");
@@ -120,7 +127,7 @@ inline int encode_2d(CUtensorMap* out, const void* base, int type, uint64_t dim0
   }
   slot.key = key;
   slot.map = *out;
-  slot.used = true;
+  set.tag[victim] = tag;
   return OG_OK;
 }
 
