@@ -14,6 +14,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <mutex>
 
 #include <cuda.h>
@@ -291,8 +292,9 @@ thread_local PlanMemo plan_memo;
 // A launch's parameter block is a function of the bound GEMM, the caller's
 // pointers and the wait limit.  Loops that run the same buffers again and
 // again (serving, benchmarks) find theirs here and skip the pointer checks,
-// the tensor-map look-ups and the fill: per thread, sixteen blocks indexed by
-// a hash of the output address.
+// the tensor-map look-ups and the fill: per thread, 256 blocks indexed by a
+// hash of the output address (about 280 KB, allocated by a thread's first
+// launch), enough for loops that rotate a hundred-odd buffer sets past L2.
 struct ParamsMemo {
   bool valid = false;
   unsigned generation = 0;
@@ -308,7 +310,8 @@ struct ParamsMemo {
            status == status_word && scaled_out == (a != nullptr) && (!a || alpha == *a) && wait_limit == limit;
   }
 };
-thread_local ParamsMemo params_memo[16];
+constexpr unsigned PARAMS_MEMO_BITS = 8;
+thread_local std::unique_ptr<ParamsMemo[]> params_memo;
 
 int launch_impl(const OgGemm* g, const LaunchPointers& io, int device, void* stream, int* status_word,
                 int want_scaled, const float* alpha = nullptr) {
@@ -327,7 +330,9 @@ int launch_impl(const OgGemm* g, const LaunchPointers& io, int device, void* str
   if (want_scaled >= 0 && int(p.format->scaled) != want_scaled)
     return fail(OG_ERR_LAUNCH, "dtype %.16s does not belong to this library", g->dtype);
   const unsigned long long wait_limit = current_wait_limit_ns();
-  ParamsMemo& memo = params_memo[(uint32_t(reinterpret_cast<uintptr_t>(io.c) >> 9) * 0x9E3779B1u) >> 28];
+  if (!params_memo) params_memo.reset(new ParamsMemo[1u << PARAMS_MEMO_BITS]());
+  ParamsMemo& memo =
+      params_memo[(uint32_t(reinterpret_cast<uintptr_t>(io.c) >> 9) * 0x9E3779B1u) >> (32 - PARAMS_MEMO_BITS)];
   const bool remembered = memo.matches(plan_memo.generation, io, status_word, alpha, wait_limit);
   if (!remembered) {
     const int rc = check_pointers(*g, p, io, alpha, why, sizeof why);
