@@ -106,6 +106,19 @@ def label(config):
     return text
 
 
+def merged_entry(existing, name, m, n, k, best, measured, dependent):
+    """The store entry after a tuning run: the winner lands in the field of its
+    launch mode, whatever the entry holds for the other mode stays."""
+    entry = dict(existing or {"dtype": name, "m": m, "n": n, "k": k})
+    if dependent:
+        entry.update(config_dependent=best, measured_dependent=measured)
+        entry.setdefault("config", best)  # the schema's one mandatory configuration
+        entry.setdefault("measured", measured)
+    else:
+        entry.update(config=best, measured=measured)
+    return entry
+
+
 def tune(name, m, n, k, verbose=False, window_ms=15.0, final_ms=60.0, dependent=False):
     """Sweep one (dtype, shape), store the winner and return its configuration.
 
@@ -183,13 +196,7 @@ def _tune(name, m, n, k, impl, library, verbose, window_ms, final_ms, dependent)
     base = harness.timed(baseline, window_ms=final_ms, repeats=3) if baseline else None
     log(f"best: {label(best)}  ({len(ranked)} timed, {rejected} failed correctness)")
     measured = {"us": round(us, 3), "cublas_us": base and round(base, 3), "env": harness.env_stamp()}
-    entry = dict(stored_entry(name, m, n, k) or {"dtype": name, "m": m, "n": n, "k": k})
-    if dependent:
-        entry.update(config_dependent=best, measured_dependent=measured)
-        entry.setdefault("config", best)  # the schema's one mandatory configuration
-    else:
-        entry.update(config=best, measured=measured)
-    path = write_entry(impl, entry)
+    path = write_entry(impl, merged_entry(stored_entry(name, m, n, k), name, m, n, k, best, measured, dependent))
     if base:
         log(f"kernel {us:.2f}us  cuBLAS {base:.2f}us  {base / us:.3f}x; stored in {path}")
     else:

@@ -296,3 +296,17 @@ def test_heuristic_makes_the_tuned_pair_or_single_choice_on_most_shipped_entries
                 same += bool(ruled["use_2cta"]) == bool(tuned["use_2cta"])
                 total += 1
         assert total >= 300 and same >= 0.8 * total, (dependent, same, total)
+
+
+def test_tuning_one_launch_mode_keeps_the_other_modes_configuration():
+    from opengemm_b200 import tune
+
+    fat, wide = {"output_n": 256}, {"output_n": 64}
+    first = tune.merged_entry(None, "mxfp4", 64, 7168, 8192, fat, {"us": 5.4}, dependent=False)
+    assert first == {"dtype": "mxfp4", "m": 64, "n": 7168, "k": 8192, "config": fat, "measured": {"us": 5.4}}
+    both = tune.merged_entry(first, "mxfp4", 64, 7168, 8192, wide, {"us": 10.7}, dependent=True)
+    assert both["config"] == fat and both["config_dependent"] == wide and both["measured_dependent"] == {"us": 10.7}
+    again = tune.merged_entry(both, "mxfp4", 64, 7168, 8192, dict(fat, supergroup=1), {"us": 5.3}, dependent=False)
+    assert again["config"]["supergroup"] == 1 and again["config_dependent"] == wide and again["measured"] == {"us": 5.3}
+    alone = tune.merged_entry(None, "mxfp4", 64, 7168, 8192, wide, {"us": 10.7}, dependent=True)
+    assert alone["config"] == wide and alone["config_dependent"] == wide  # a store entry always has `config`
